@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the SR-AdamW optimizer step (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: a 1,073,741,824-element bf16 parameter shard per GPU with fp32 moments, gradients
+~N(0,1e-3), step counter at 100 (the "pure memory-bound roofline case").  A step is one
+``AdamW.step()`` over that shard; with N > 1 every rank owns one such shard of an N-times larger
+flat parameter space (ZeRO-1) and the step ends with the all-gather of the updated parameters.
+
+  value     params updated / s, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e       same metric with parameters, gradients and moments in pinned HOST memory, streamed
+            through the GPU by ``AdamW.step()`` (copies inside the timed region)
+  roofline  algorithmic bytes (22 B/element) / kernel time against the measured HBM copy peak
+  cpu_baseline / --impl reference
+            the CPU restatement of the reference step (oracle/, C + OpenMP, all host threads) on
+            a bounded sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sr_adamw_params_per_s"
+UNIT = "params/s"
+ELEMS_PER_GPU = 1 << 30
+BYTES_PER_ELEM = 22            # read p2 g2 m4 v4, write p2 m4 v4
+HP = dict(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+START_STEP = 99                # the timed steps start at t = 100
+# DRAM bytes per element of the fused kernel (bf16 p/g, fp32 moments) measured with ncu
+# (dram__bytes_read.sum + dram__bytes_write.sum over one launch; see profiles/).  None until a
+# capture exists.
+NCU_DRAM_BYTES_PER_ELEM = None
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.1] or [r for _, r in self.rows[-3:]]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(seconds=12.0, sample_elems=1 << 26, warmup=1, steps=None):
+    """The CPU restatement of the reference step on all host threads, on a sample of the
+    workload (same dtypes and distributions)."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(0)
+    n = sample_elems
+
+    def normal(scale):
+        out = np.empty(n, np.float32)
+        blk = 1 << 22
+        for lo in range(0, n, blk):
+            out[lo:lo + blk] = rng.standard_normal(min(blk, n - lo), dtype=np.float32) * scale
+        return out
+
+    p = oracle.f32_to_bf16_bits_rn(normal(0.02))
+    g = oracle.f32_to_bf16_bits_rn(normal(1e-3))
+    m = normal(1e-3)
+    v = np.abs(normal(1e-6))
+    threads = oracle.num_threads()
+    times, k = [], 0
+    t_end = time.time() + seconds
+    while True:
+        h = oracle.make_hyper(HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"], START_STEP + 1 + k)
+        t0 = time.perf_counter()
+        oracle.adamw_sr(p, g, m, v, oracle.BF16, oracle.BF16, oracle.F32, h, seed=0, tensor_id=0)
+        dt = time.perf_counter() - t0
+        k += 1
+        if k > warmup:
+            times.append(dt)
+        if steps is not None:
+            if len(times) >= steps:
+                break
+        elif time.time() > t_end and len(times) >= 3:
+            break
+    mean = sum(times) / len(times)
+    return {"value": n / mean, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{n} elements (1/{ELEMS_PER_GPU // n} of one shard), bf16 p/g + fp32 moments, "
+                      f"{len(times)} steps of the C+OpenMP restatement in oracle/, {threads} threads",
+            "ms_per_step": mean * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_baseline(steps=args.steps, warmup=max(args.warmup, 1))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config 2: bf16 parameter shard with fp32 moments, t=100, on host cores",
+                       "elements_per_step": 1 << 26},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def synth_on_device(n, device, seed):
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    blk = 1 << 28
+    p = torch.empty(n, dtype=torch.bfloat16, device=device)
+    grad = torch.empty(n, dtype=torch.bfloat16, device=device)
+    m = torch.empty(n, dtype=torch.float32, device=device)
+    v = torch.empty(n, dtype=torch.float32, device=device)
+    for lo in range(0, n, blk):
+        hi = min(n, lo + blk)
+        p[lo:hi] = torch.randn(hi - lo, device=device, generator=g) * 0.02
+        grad[lo:hi] = torch.randn(hi - lo, device=device, generator=g) * 1e-3
+        m[lo:hi] = torch.randn(hi - lo, device=device, generator=g) * 1e-3
+        v[lo:hi] = (torch.randn(hi - lo, device=device, generator=g) * 1e-6).abs()
+    return p, grad, m, v
+
+
+def host_mem_available_bytes():
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) * 1024
+    except Exception:
+        pass
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--elems", type=int, default=ELEMS_PER_GPU, help="elements per GPU (default 2^30)")
+    ap.add_argument("--e2e-steps", type=int, default=4)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from ramtorch_b200 import AdamW, _native as N
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n = args.elems
+    warmup = max(args.warmup, 3)
+
+    # ---------------------------------------------------------------- resident step (value)
+    flat = torch.empty(n * world, dtype=torch.bfloat16, device=device)   # the replicated parameters
+    shard = flat[rank * n:(rank + 1) * n]
+    p0, grad, m0, v0 = synth_on_device(n, device, seed=rank)
+    shard.copy_(p0)
+    del p0
+    opt = AdamW([shard], dtype=torch.float32, storage_device=device, seed=0, sync=False, **HP)
+    st = opt.state[shard]
+    st["ema"].copy_(m0); st["ema_squared"].copy_(v0); st["step"] = START_STEP
+    del m0, v0
+    shard.grad = grad
+
+    def one_step():
+        opt.step()
+        if world > 1:
+            dist.all_gather_into_tensor(flat, shard)
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+    launches0 = N.stats()["kernel_launches"]
+    t_wall0 = time.time()
+    ev[0].record()
+    for k in range(args.steps):
+        opt.step()
+        ev[3 * k + 1].record()
+        if world > 1:
+            dist.all_gather_into_tensor(flat, shard)
+        ev[3 * k + 2].record()
+        ev[3 * k + 3].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    launches = N.stats()["kernel_launches"] - launches0
+    total_ms = ev[0].elapsed_time(ev[3 * args.steps])
+    upd_ms = sum(ev[3 * k].elapsed_time(ev[3 * k + 1]) for k in range(args.steps)) / args.steps
+    ag_ms = sum(ev[3 * k + 1].elapsed_time(ev[3 * k + 2]) for k in range(args.steps)) / args.steps
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    if world > 1:
+        t = torch.tensor([total_ms, upd_ms, ag_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, upd_ms, ag_ms = t.tolist()
+    ms_per_step = total_ms / args.steps
+    value = n * world / (ms_per_step * 1e-3)
+
+    # the kernel's own duration: steps are enqueued back to back, so the update interval between
+    # consecutive events is the kernel (plus a 48-byte hyper-parameter copy)
+    peak, which = measured_peak()
+    achieved = BYTES_PER_ELEM * n / (upd_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": which,
+                "traffic": None if NCU_DRAM_BYTES_PER_ELEM is None else NCU_DRAM_BYTES_PER_ELEM * n,
+                "algorithmic_bytes": BYTES_PER_ELEM * n, "kernel_ms": upd_ms,
+                "frac_of_nominal_8TBs": achieved / 8000.0}
+
+    # ---------------------------------------------------------------- end to end from host memory
+    e2e = None
+    if not args.no_e2e:
+        del opt, st
+        shard.grad = None
+        del grad, flat, shard
+        torch.cuda.empty_cache()
+        n_host = n
+        budget = host_mem_available_bytes() // max(world, 1)
+        while n_host * 12 * 1.3 > budget and n_host > (1 << 24):
+            n_host //= 2
+        hp_, hg = (torch.empty(n_host, dtype=torch.bfloat16, pin_memory=True) for _ in range(2))
+        # storage_device="cpu" (the reference default): moments in pinned host memory
+        hopt = AdamW([hp_], dtype=torch.float32, storage_device="cpu", seed=0, **HP)
+        hst = hopt.state[hp_]
+        dp, dg, dm, dv = synth_on_device(n_host, device, seed=100 + rank)
+        for h, d in ((hp_, dp), (hg, dg), (hst["ema"], dm), (hst["ema_squared"], dv)):
+            h.copy_(d)
+        hst["step"] = START_STEP
+        del dp, dg, dm, dv
+        torch.cuda.empty_cache()
+        hp_.grad = hg
+        hopt.step()   # warm-up: creates the pipeline streams and the staging ring
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s0 = N.stats()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            hopt.step()              # returns when the results are back in host memory
+            _ = float(hp_[0])        # host read of the step's result
+        e1.record()
+        torch.cuda.synchronize()
+        s1 = N.stats()
+        e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = t.item()
+        h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) // args.e2e_steps
+        d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) // args.e2e_steps
+        e2e = {"value": n_host * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "elements_per_gpu": n_host,
+               "h2d_gbs": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs": d2h / (e2e_ms * 1e-3) / 1e9,
+               "steps": args.e2e_steps, "chunk_elems": hopt.offload_chunk_elems,
+               "ring_depth": hopt.offload_ring_depth}
+
+    base = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        base = cpu_baseline()
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "config 2: 2^30-element bf16 parameter shard per GPU, fp32 moments, "
+                                       "bf16 grads ~N(0,1e-3), t=100" +
+                                       (", ZeRO-1 all-gather of updated parameters inside the step" if world > 1 else ""),
+                           "elements_per_gpu": n, "l2": "inputs (12 GiB per GPU) far exceed L2; no flush needed",
+                           "parallelism": f"zero1x{world}" if world > 1 else "single"},
+                "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
+                "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
+                "update_only_value": n * world / (upd_ms * 1e-3)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

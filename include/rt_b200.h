@@ -1,0 +1,204 @@
+/*
+ * rt_b200.h — C ABI of librt_b200.so: the stochastic-rounding AdamW optimizer step of
+ * RamTorch (ramtorch/stochastic_optimizers/adamw.py) as hand-written CUDA for sm_100a.
+ *
+ * Conventions
+ *   - Every entry point returns int: 0 = ok, negative = argument error found on the host
+ *     before any launch (RT_E_*), positive = a cudaError_t passed through.
+ *     rt_last_error() returns a thread-local message for the last non-zero return.
+ *   - All tensor memory belongs to the caller.  The library receives raw pointers, element
+ *     counts, dtype codes and a cudaStream_t (passed as void*; NULL = the legacy default
+ *     stream).  It keeps nothing beyond what a plan handle documents.
+ *   - Calls are asynchronous with respect to the host unless stated otherwise: work is
+ *     enqueued on the given stream and the caller synchronises.
+ *   - There is no CPU implementation behind any entry point.
+ *
+ * Arithmetic contract (identical in the CUDA kernels and in the CPU checker under oracle/)
+ *   g, m, v, p are widened to fp32.  With the scalars of rt_hyper:
+ *     m' = fma(one_minus_beta1, g, m * beta1)                    adamw.py:190
+ *     v' = fma(one_minus_beta2 * g, g, v * beta2)                adamw.py:191
+ *     den = sqrt(v') / bias_correction2_sqrt + eps               adamw.py:193-195
+ *     p' = (apply_decay ? p * decay : p) + (neg_step_size * m') / den   adamw.py:197-200
+ *   every operation rounded to nearest-even fp32 separately except the two fma's.
+ *   Write-back (adamw.py:204-222): a bf16 destination is stochastically rounded,
+ *     out16 = ((bits(x) + r16) & 0xFFFF0000) >> 16                adamw.py:6-30
+ *   an fp32 destination is copied, an fp16 destination is rounded to nearest-even.
+ *
+ * Random bits
+ *   r16 comes from Philox4x32-10 (Salmon et al., SC'11) with
+ *     key     = (seed & 0xFFFFFFFF, seed >> 32)
+ *     counter = (i >> 3, tensor_id, step, stream)       i = element index inside its tensor
+ *   stream 0 rounds the parameter, 1 exp_avg ("ema"), 2 exp_avg_sq ("ema_squared").
+ *   The 4 output words hold 8 draws; element i takes draw j = i & 7:
+ *     word = out[j >> 1];  r16 = (j & 1) ? word >> 16 : word & 0xFFFF.
+ *   The bits depend only on (seed, step, tensor_id, i), never on launch geometry, chunking,
+ *   residency (HBM or host) or the number of GPUs.
+ *   The reference draws from torch.Generator seeded step+42 / +69 / +420 (adamw.py:206-218);
+ *   that stream is not reproducible across devices and is replaced on purpose.
+ */
+#ifndef RT_B200_H
+#define RT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes */
+enum { RT_BF16 = 0, RT_F32 = 1, RT_F16 = 2 };
+
+/* host-side argument errors */
+enum {
+  RT_E_NULL = -1,       /* required pointer is NULL */
+  RT_E_DTYPE = -2,      /* dtype code outside RT_BF16..RT_F16 */
+  RT_E_SIZE = -3,       /* negative or too large element count */
+  RT_E_ALIGN = -4,      /* pointer not aligned to its element size */
+  RT_E_PLAN = -5,       /* bad plan handle / plan misuse */
+  RT_E_CONFIG = -6,     /* bad pipeline configuration */
+  RT_E_DEVICE = -7      /* no usable CUDA device */
+};
+
+/*
+ * Per-step scalars, already reduced to fp32 the way the reference reduces its Python
+ * doubles when they meet fp32 tensors (adamw.py:186-200).  With t = step (after the
+ * increment of adamw.py:177), ss = lr / (1 - beta1^t):
+ */
+typedef struct rt_hyper {
+  float beta1;                  /* f32(beta1) */
+  float one_minus_beta1;        /* f32(1 - beta1) */
+  float beta2;                  /* f32(beta2) */
+  float one_minus_beta2;        /* f32(1 - beta2) */
+  float bias_correction2_sqrt;  /* f32(sqrt(1 - beta2^t)) */
+  float eps;                    /* f32(eps) */
+  float decay;                  /* f32(1 - ss * weight_decay) */
+  float neg_step_size;          /* f32(-ss) */
+  float centralization;         /* f32(c); 0 disables (adamw.py:179-184) */
+  uint32_t apply_decay;         /* weight_decay != 0 (adamw.py:197) */
+  uint32_t step;                /* t; also the Philox counter word 2 */
+  uint32_t reserved;
+} rt_hyper;
+
+/* Fill an rt_hyper from the constructor-level values, in double precision, as
+ * adamw.py:173-188 does.  Pure host arithmetic. */
+int rt_hyper_fill(rt_hyper* out, double lr, double beta1, double beta2, double eps,
+                  double weight_decay, double centralization, uint32_t step);
+
+const char* rt_last_error(void);
+/* Library / kernel identification, e.g. "rt_b200 0.1 sm_100a". */
+const char* rt_version(void);
+
+/* Optional per-call debug taps.  Any pointer may be NULL.
+ *   rand_*  : injected 16-bit draws (device, one uint16 per element) used INSTEAD of Philox.
+ *   f32_*   : device buffers receiving the fp32 values p', m', v' before the write-back.
+ * Production calls pass NULL for the whole struct. */
+typedef struct rt_debug {
+  const uint16_t* rand_p;
+  const uint16_t* rand_m;
+  const uint16_t* rand_v;
+  float* f32_p;
+  float* f32_m;
+  float* f32_v;
+} rt_debug;
+
+/*
+ * a1 — stochastic rounding alone: replaces copy_stochastic_(target, source, seed)
+ * (adamw.py:6-30).  source: n fp32 on the device; target: n bf16 on the device.
+ * rand16 != NULL injects the draws, otherwise Philox (seed, tensor_id, step, stream).
+ */
+int rt_sr_round_bf16(void* target_bf16, const float* source_f32, int64_t n,
+                     const uint16_t* rand16, uint64_t seed, uint32_t tensor_id,
+                     uint32_t step, uint32_t stream_id, void* cuda_stream);
+
+/*
+ * a3-a6 — one fused step over ONE contiguous tensor resident in device memory: replaces the
+ * body of AdamW.step for one parameter (adamw.py:160-222).  p, m, v are updated in place.
+ * index0 is the tensor-local index of element 0 of the pointers given (non-zero when the
+ * caller passes a slice of a larger tensor, e.g. a streamed chunk or a ZeRO shard); it must
+ * be a multiple of 8.
+ */
+int rt_adamw_sr_flat(void* p, const void* g, void* m, void* v, int64_t n,
+                     int p_dtype, int g_dtype, int state_dtype,
+                     const rt_hyper* hyper, uint64_t seed, uint32_t tensor_id,
+                     int64_t index0, const rt_debug* debug, void* cuda_stream);
+
+/*
+ * Multi-tensor plan: the tensor table of an optimizer (one row per parameter that has a
+ * gradient), uploaded to the device once and reused every step while the pointers stay
+ * the same.  Replaces the Python loop of adamw.py:111-232 (~25 launches and up to three
+ * generator constructions per tensor) by one launch per dtype combination.
+ */
+typedef struct rt_tensor_desc {
+  void* p;
+  const void* g;
+  void* m;
+  void* v;
+  int64_t numel;
+  int64_t index0;       /* tensor-local index of element 0 (multiple of 8) */
+  uint32_t tensor_id;   /* Philox counter word 1 */
+  uint32_t hyper_index; /* row of the hyper table passed at step time */
+  uint8_t p_dtype, g_dtype, state_dtype, reserved0;
+  uint32_t row_len;     /* elements per row for centralization; 0 = whole tensor is one row */
+} rt_tensor_desc;
+
+typedef struct rt_plan rt_plan;
+
+/* Build a plan for `count` tensors on CUDA device `device`.  Allocates device memory for the
+ * tables with cudaMalloc (freed by rt_plan_destroy).  Synchronous. */
+int rt_plan_create(rt_plan** out, const rt_tensor_desc* tensors, int64_t count, int device);
+int rt_plan_destroy(rt_plan* plan);
+/* Replace the gradient pointers only (grads are re-allocated by autograd after
+ * zero_grad(set_to_none=True)); `g` has one entry per plan tensor, in plan order. */
+int rt_plan_set_grads(rt_plan* plan, const void* const* g, void* cuda_stream);
+/* Number of kernel launches one rt_adamw_sr_multi call issues for this plan. */
+int rt_plan_launches(const rt_plan* plan);
+/* One optimizer step over every tensor of the plan.  hyper[] has hyper_count rows
+ * (<= 1024); each tensor uses row hyper_index. */
+int rt_adamw_sr_multi(rt_plan* plan, const rt_hyper* hyper, int hyper_count,
+                      uint64_t seed, void* cuda_stream);
+
+/*
+ * Host-offloaded step (adamw.py:152-170, 204-222 when parameters and/or state live in CPU
+ * RAM): streams one tensor through the GPU in chunks.  Each of p, g, m, v may be a pinned
+ * host pointer or a device pointer; host-resident ones are staged through the ring of
+ * device buffers in `staging` (at least ring_depth * chunk_elems * bytes-per-element of
+ * the host-resident tensors).  H2D, kernel and D2H run on three library-owned side
+ * streams, ordered by events; `cuda_stream` is made to wait for the pipeline's completion
+ * and the pipeline waits for work already enqueued on `cuda_stream`.
+ */
+typedef struct rt_offload_cfg {
+  int64_t chunk_elems;  /* multiple of 8; 0 = default (128 Mi elements / 8) */
+  int ring_depth;       /* 2..8; 0 = default 3 */
+  void* staging;        /* device memory */
+  int64_t staging_bytes;
+} rt_offload_cfg;
+
+int64_t rt_offload_staging_bytes(int64_t chunk_elems, int ring_depth, int p_dtype,
+                                 int g_dtype, int state_dtype, int p_on_host,
+                                 int g_on_host, int m_on_host, int v_on_host);
+
+int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int64_t n,
+                        int p_dtype, int g_dtype, int state_dtype,
+                        const rt_hyper* hyper, uint64_t seed, uint32_t tensor_id,
+                        const rt_offload_cfg* cfg, void* cuda_stream);
+
+/* Pin / unpin caller-owned host memory (cudaHostRegister) so the copy engines can stream it;
+ * needed for shared-memory parameter storage that arrives unpinned in worker processes. */
+int rt_host_register(void* ptr, int64_t bytes);
+int rt_host_unregister(void* ptr);
+
+/* Counters since load: kernels launched by this library, bytes copied H2D and D2H by the
+ * offload pipeline. */
+typedef struct rt_stats {
+  uint64_t kernel_launches;
+  uint64_t h2d_bytes;
+  uint64_t d2h_bytes;
+  uint64_t h2d_copies;
+  uint64_t d2h_copies;
+} rt_stats;
+int rt_query_stats(rt_stats* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RT_B200_H */

@@ -1,0 +1,60 @@
+// Internal declarations shared by the translation units of librt_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <string>
+
+#include "../../include/rt_b200.h"
+
+namespace rt {
+
+// One row of the device-resident tensor table (80 bytes).
+struct DevTensor {
+  void* p;
+  const void* g;
+  void* m;
+  void* v;
+  const float* row_mean;  // centralization * mean of each gradient row, or nullptr
+  int64_t numel;
+  int64_t index0;         // tensor-local index of element 0 (multiple of 8)
+  uint32_t tensor_id;
+  uint32_t hyper_index;
+  uint32_t row_len;       // elements per row of row_mean (0: one row)
+  uint32_t flags;         // kVecOk
+};
+constexpr uint32_t kVecOk = 1u;  // all four pointers are 16-byte aligned
+
+constexpr int kThreads = 256;
+constexpr int kChunkElems = kThreads * 8 * 4;  // elements one CTA walks through
+
+// error plumbing -------------------------------------------------------------
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+#define RT_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+struct Stats {
+  std::atomic<uint64_t> kernel_launches{0}, h2d_bytes{0}, d2h_bytes{0}, h2d_copies{0}, d2h_copies{0};
+};
+Stats& stats();
+
+inline int dtype_size(int d) { return d == RT_F32 ? 4 : 2; }
+inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
+
+// Launch the fused kernel.  Either (table, chunks, hypers) describe a multi-tensor launch of
+// nblocks chunks, or they are null and `one`/`one_h` describe a single tensor.
+int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* chunks,
+                 const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
+                 uint64_t seed, int64_t nblocks, cudaStream_t stream);
+int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
+                       uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
+int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,
+                  int pd, int gd, int sd, const rt_hyper* h, int64_t index0);
+uint32_t vec_flag(const void* p, const void* g, const void* m, const void* v);
+
+}  // namespace rt

@@ -1,0 +1,320 @@
+"""AdamW with bf16 stochastic rounding — drop-in for ``ramtorch.stochastic_optimizers.adamw``.
+
+Same constructor, same ``state[p]`` keys (``step``, ``ema``, ``ema_squared``), same update rule as
+the reference (ramtorch/stochastic_optimizers/adamw.py:33-234), but ``step()`` hands the whole
+parameter list to ``librt_b200.so``:
+
+* tensors whose parameter, gradient and moments all sit in HBM go through ONE fused
+  multi-tensor kernel launch per dtype combination (the reference issues ~25 ATen launches and
+  up to three generator constructions per tensor, adamw.py:160-222);
+* tensors with any of them in CPU RAM go through the chunked copy-in / update / copy-out
+  pipeline on side streams (the reference serialises ``.to(device)`` → math → ``.copy_`` on one
+  stream, adamw.py:160-170, :204-222).
+
+Differences from the reference that a user can observe, all deliberate:
+
+* random bits come from a counter-based Philox stream keyed by ``(seed, step, tensor id, element
+  index)`` instead of ``torch.Generator(seed=step+42/69/420)`` (adamw.py:206-218), so results do
+  not depend on device, launch geometry, chunking or world size;
+* there is no CPU path: without a CUDA device ``step()`` raises;
+* one stream synchronisation at the end of ``step()`` replaces the device-wide synchronisations
+  every ``chunk_size`` parameters (adamw.py:227-232); ``chunk_size`` is accepted and ignored.
+"""
+from __future__ import annotations
+
+import ctypes
+import warnings
+
+import torch
+from torch.optim import Optimizer
+
+from .. import _native as N
+from ..functional import sr_round_bf16_
+
+_PARAM_IDS_KEY = "rt_param_ids"
+
+
+def copy_stochastic_(target: torch.Tensor, source: torch.Tensor, seed=0):
+    """bf16 stochastic rounding of an fp32 CUDA tensor into ``target`` (adamw.py:6-30).
+
+    ``out = (bits(source) + r16) & 0xFFFF0000`` with ``r16`` uniform on [0, 65536).  The draws
+    come from Philox keyed by ``seed`` and the element index."""
+    with torch.no_grad():
+        src = source.detach()
+        if src.dtype != torch.float32:
+            raise ValueError("source must be float32")
+        src = src.contiguous()
+        if target.is_contiguous():
+            sr_round_bf16_(target.detach(), src, seed=int(seed))
+        else:
+            tmp = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+            sr_round_bf16_(tmp, src, seed=int(seed))
+            target.copy_(tmp)
+
+
+class _DevicePlan:
+    """A live ``rt_plan`` handle plus the signature it was built from."""
+
+    def __init__(self, device_index: int, signature, descs):
+        self.signature = signature
+        self.handle = ctypes.c_void_p()
+        arr = (N.TensorDesc * len(descs))(*descs)
+        N.check(N.lib().rt_plan_create(ctypes.byref(self.handle), arr, len(descs), device_index),
+                "rt_plan_create")
+        self.launches = N.lib().rt_plan_launches(self.handle)
+        self.grad_ptrs = (N.c_void_p * len(descs))()
+
+    def close(self):
+        if self.handle:
+            N.lib().rt_plan_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class AdamW(Optimizer):
+    r"""
+    Arguments (identical to the reference, adamw.py:57-69):
+        params: iterable of parameters or dicts defining parameter groups.
+        lr: learning rate (default 1e-3).
+        betas: coefficients of the running averages (default (0.9, 0.999)).
+        eps: added to the denominator (default 1e-8).
+        weight_decay: decoupled weight decay, scaled by the bias-corrected step size as in the
+            reference (default 1e-2).
+        centralization: gradient centralization factor (default 0).
+        chunk_size: accepted for compatibility; the fused path needs no periodic sync.
+        dtype: dtype of ``ema`` / ``ema_squared`` (default bf16).
+        storage_device: where the moments live; the string ``"cpu"`` means pinned host memory.
+
+    Keyword-only additions:
+        seed: Philox key of the stochastic-rounding stream (default 0).
+        offload_chunk_elems: elements per streamed chunk for host-resident tensors.
+        offload_ring_depth: staging slots of the streaming pipeline (2..8).
+        sync: wait for the step to finish before returning, as the reference does (default True).
+    """
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
+                 centralization=0, chunk_size=64, dtype=torch.bfloat16, storage_device="cpu",
+                 *, seed=0, offload_chunk_elems=1 << 24, offload_ring_depth=3, sync=True):
+        if dtype not in N.DTYPE_CODE:
+            raise ValueError(f"unsupported state dtype {dtype}: bf16, fp32 or fp16")
+        if offload_chunk_elems <= 0 or offload_chunk_elems % 8:
+            raise ValueError("offload_chunk_elems must be a positive multiple of 8")
+        if not 2 <= offload_ring_depth <= 8:
+            raise ValueError("offload_ring_depth must be in 2..8")
+        self._next_tensor_id = 0
+        self._tensor_ids = {}
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                        centralization=centralization)
+        super().__init__(params, defaults)
+
+        self.chunk_size = chunk_size
+        self.optim_state_dtype = dtype
+        self.optim_state_device = storage_device
+        self.seed = int(seed)
+        self.offload_chunk_elems = int(offload_chunk_elems)
+        self.offload_ring_depth = int(offload_ring_depth)
+        self.sync = bool(sync)
+        self._plans = {}      # cuda device index -> _DevicePlan
+        self._staging = {}    # cuda device index -> uint8 tensor
+        self._keepalive = []
+        self._warned_pageable = False
+        self.last_step_info = {}
+
+        # eager state, as adamw.py:84-104; "cpu" (the string) means pinned, and the pinned
+        # moments of all parameters share two allocations instead of two per tensor
+        fresh = [p for g in self.param_groups for p in g["params"] if not self.state[p]]
+        self._allocate_states(fresh)
+
+    # ------------------------------------------------------------------ bookkeeping
+    def add_param_group(self, param_group):
+        super().add_param_group(param_group)
+        group = self.param_groups[-1]
+        ids = group.get(_PARAM_IDS_KEY)
+        if ids is not None and len(ids) != len(group["params"]):
+            raise ValueError(f"{_PARAM_IDS_KEY} must list one id per parameter of the group")
+        for k, p in enumerate(group["params"]):
+            if ids is not None:
+                self._tensor_ids[p] = int(ids[k])
+            else:
+                self._tensor_ids[p] = self._next_tensor_id
+                self._next_tensor_id += 1
+
+    def _allocate_states(self, params):
+        """``step = 0`` and zero moments of ``dtype`` on ``storage_device`` (adamw.py:85-104)."""
+        if not params:
+            return
+        dtype, dev = self.optim_state_dtype, self.optim_state_device
+        if isinstance(dev, str) and dev == "cpu":
+            esize = torch.empty((), dtype=dtype).element_size()
+            offs, total = [], 0
+            for p in params:
+                offs.append(total)
+                total += (p.numel() * esize + 255) // 256 * 256
+            pools = [torch.zeros(max(total, 256), dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+            for p, off in zip(params, offs):
+                nbytes = p.numel() * esize
+                st = self.state[p]
+                st["step"] = 0
+                st["ema"], st["ema_squared"] = (
+                    pool[off:off + nbytes].view(dtype).view(p.shape) for pool in pools)
+        else:
+            for p in params:
+                st = self.state[p]
+                st["step"] = 0
+                st["ema"] = torch.zeros(p.shape, dtype=dtype, device=dev)
+                st["ema_squared"] = torch.zeros(p.shape, dtype=dtype, device=dev)
+
+    def _staging_for(self, index: int, nbytes: int) -> torch.Tensor:
+        buf = self._staging.get(index)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", index))
+            self._staging[index] = buf
+        return buf
+
+    # ------------------------------------------------------------------ the step
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            loss = closure()
+        if not torch.cuda.is_available():
+            raise RuntimeError("ramtorch_b200.AdamW needs a CUDA device: there is no CPU fallback")
+        lib = N.lib()
+        self._keepalive.clear()
+
+        resident = {}   # device index -> list of (p, grad, ema, ema_sq, tensor_id, hyper_index)
+        streamed = []   # (device index, p, grad, ema, ema_sq, tensor_id, hyper_index)
+        hyper_rows, hyper_index = [], {}
+        late = []
+        for gi, group in enumerate(self.param_groups):
+            for p in group["params"]:
+                grad = p.grad
+                if grad is None:
+                    continue
+                if grad.is_sparse:
+                    raise RuntimeError("AdamW does not support sparse gradients")
+                if not self.state[p]:
+                    late.append(p)
+        self._allocate_states(late)  # lazy state for parameters added late (adamw.py:125-148)
+
+        for gi, group in enumerate(self.param_groups):
+            if group["centralization"] != 0:
+                raise NotImplementedError("centralization != 0 is not available in this build yet")
+            for p in group["params"]:
+                grad = p.grad
+                if grad is None:
+                    continue
+                state = self.state[p]
+                state["step"] += 1
+                key = (gi, state["step"])
+                hi = hyper_index.get(key)
+                if hi is None:
+                    hi = hyper_index[key] = len(hyper_rows)
+                    hyper_rows.append(N.make_hyper(group["lr"], group["betas"], group["eps"],
+                                                   group["weight_decay"], state["step"],
+                                                   group["centralization"]))
+                ema, ema_sq = state["ema"], state["ema_squared"]
+                pd = p.data
+                if not pd.is_contiguous():
+                    raise ValueError("parameters must be contiguous for the in-place fused update")
+                if not grad.is_contiguous():
+                    grad = grad.contiguous()
+                    self._keepalive.append(grad)
+                if not (ema.is_contiguous() and ema_sq.is_contiguous()):
+                    raise ValueError("optimizer state tensors must be contiguous")
+                if ema.dtype != ema_sq.dtype:
+                    raise ValueError("ema and ema_squared must share a dtype")
+                for t, name in ((pd, "parameter"), (grad, "gradient"), (ema, "state")):
+                    if t.dtype not in N.DTYPE_CODE:
+                        raise ValueError(f"unsupported {name} dtype {t.dtype}: bf16, fp32 or fp16")
+                if not (grad.numel() == ema.numel() == ema_sq.numel() == pd.numel()):
+                    raise ValueError("parameter, gradient and state sizes differ")
+                cuda_devs = {t.device.index for t in (pd, grad, ema, ema_sq) if t.is_cuda}
+                if len(cuda_devs) > 1:
+                    raise ValueError("parameter, gradient and state sit on different CUDA devices")
+                # compute device: the parameter's, or the current one for CPU parameters
+                # (adamw.py:152-157)
+                index = cuda_devs.pop() if cuda_devs else torch.cuda.current_device()
+                entry = (pd, grad, ema, ema_sq, self._tensor_ids[p], hi)
+                if pd.is_cuda and grad.is_cuda and ema.is_cuda and ema_sq.is_cuda:
+                    resident.setdefault(index, []).append(entry)
+                else:
+                    streamed.append((index,) + entry)
+
+        if len(hyper_rows) > 1024:
+            raise ValueError("more than 1024 distinct (group, step) pairs in one step")
+        hyper_arr = (N.Hyper * max(len(hyper_rows), 1))(*hyper_rows)
+        seed = self.seed & (2 ** 64 - 1)
+        used = set()
+        launches = 0
+
+        for index, entries in resident.items():
+            used.add(index)
+            with torch.cuda.device(index):
+                plan = self._plan_for(index, entries)
+                for k, e in enumerate(entries):
+                    plan.grad_ptrs[k] = e[1].data_ptr()
+                stream = N.stream_ptr(index)
+                N.check(lib.rt_plan_set_grads(plan.handle, plan.grad_ptrs, stream), "rt_plan_set_grads")
+                N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(hyper_rows), seed, stream),
+                        "rt_adamw_sr_multi")
+                launches += plan.launches
+
+        for index, pd, grad, ema, ema_sq, tid, hi in streamed:
+            used.add(index)
+            host = [not t.is_cuda for t in (pd, grad, ema, ema_sq)]
+            if not self._warned_pageable:
+                for t, h in zip((pd, grad, ema, ema_sq), host):
+                    if h and not t.is_pinned():
+                        warnings.warn("a host-resident tensor is not pinned: its copies fall back to "
+                                      "pageable transfers and do not overlap; pin it for full speed")
+                        self._warned_pageable = True
+                        break
+            codes = (N.DTYPE_CODE[pd.dtype], N.DTYPE_CODE[grad.dtype], N.DTYPE_CODE[ema.dtype])
+            chunk = min(self.offload_chunk_elems, (pd.numel() + 7) // 8 * 8)
+            need = lib.rt_offload_staging_bytes(chunk, self.offload_ring_depth, *codes, *map(int, host))
+            if need < 0:
+                N.check(int(need), "rt_offload_staging_bytes")
+            with torch.cuda.device(index):
+                staging = self._staging_for(index, max(int(need), 256))
+                cfg = N.OffloadCfg(chunk, self.offload_ring_depth, staging.data_ptr(), staging.numel())
+                N.check(lib.rt_adamw_sr_offload(pd.data_ptr(), grad.data_ptr(), ema.data_ptr(),
+                                                ema_sq.data_ptr(), pd.numel(), *codes,
+                                                ctypes.byref(hyper_arr[hi]), seed, tid,
+                                                ctypes.byref(cfg), N.stream_ptr(index)),
+                        "rt_adamw_sr_offload")
+            launches += (pd.numel() + chunk - 1) // chunk
+
+        self.last_step_info = dict(launches=launches, resident=sum(map(len, resident.values())),
+                                   streamed=len(streamed))
+        if self.sync:
+            # results are visible to the host when step() returns (adamw.py:232)
+            for index in used:
+                torch.cuda.current_stream(index).synchronize()
+            self._keepalive.clear()
+        return loss
+
+    def _plan_for(self, index, entries) -> _DevicePlan:
+        signature = [(pd.data_ptr(), ema.data_ptr(), ema_sq.data_ptr(), pd.numel(), pd.dtype,
+                      grad.dtype, ema.dtype, tid, hi) for pd, grad, ema, ema_sq, tid, hi in entries]
+        plan = self._plans.get(index)
+        if plan is not None and plan.signature == signature:
+            return plan
+        if plan is not None:
+            torch.cuda.current_stream(index).synchronize()
+            plan.close()
+        descs = []
+        for pd, grad, ema, ema_sq, tid, hi in entries:
+            d = N.TensorDesc()
+            d.p, d.g, d.m, d.v = pd.data_ptr(), grad.data_ptr(), ema.data_ptr(), ema_sq.data_ptr()
+            d.numel, d.index0, d.tensor_id, d.hyper_index = pd.numel(), 0, tid, hi
+            d.p_dtype, d.g_dtype, d.state_dtype = (N.DTYPE_CODE[pd.dtype], N.DTYPE_CODE[grad.dtype],
+                                                   N.DTYPE_CODE[ema.dtype])
+            descs.append(d)
+        plan = _DevicePlan(index, signature, descs)
+        self._plans[index] = plan
+        return plan

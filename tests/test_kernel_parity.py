@@ -1,0 +1,245 @@
+"""GPU: the CUDA kernels, called through the C ABI, against the CPU checker and the fixtures
+produced by the reference.  Integer/bit results must be identical; fp32 pre-rounding values are
+held to 1e-6 relative (cancellation-safe denominator) and in practice match bit for bit because
+every operation of the contract is a correctly rounded IEEE operation on both sides."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import CODE, TORCH_DT, bits_equal, load_golden, step_cases, synth, to_numpy, to_torch
+
+pytestmark = pytest.mark.gpu
+F = None
+
+
+def setup_module(module):
+    global F
+    from ramtorch_b200 import functional
+    F = functional
+
+
+def _hyper_pair(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, wd=0.01, step=11):
+    from ramtorch_b200 import _native as N
+    return N.make_hyper(lr, betas, eps, wd, step), oracle.make_hyper(lr, betas, eps, wd, step)
+
+
+def run_both(n, kp, kg, ks, *, seed=3, tensor_id=5, index0=0, step=11, wd=0.01, misalign=0,
+             inject=False, taps=False, data_seed=0):
+    """Run the CUDA kernel and the checker on the same seeded inputs; return both results."""
+    p, g, m, v = synth(n, kp, kg, ks, data_seed)
+    hn, ho = _hyper_pair(step=step, wd=wd)
+    dev = torch.device("cuda")
+
+    def dev_tensor(arr, kind):
+        # optional misalignment: place the data `misalign` elements into a larger buffer
+        t = to_torch(arr, kind)
+        big = torch.zeros(n + misalign + 8, dtype=t.dtype, device=dev)
+        view = big[misalign:misalign + n]
+        view.copy_(t)
+        return big, view
+
+    bp, tp = dev_tensor(p, kp); bg, tg = dev_tensor(g, kg)
+    bm, tm = dev_tensor(m, ks); bv, tv = dev_tensor(v, ks)
+    rand_np = (None, None, None)
+    rand_t = (None, None, None)
+    if inject:
+        rng = np.random.default_rng(99)
+        rand_np = tuple(rng.integers(0, 65536, n, dtype=np.uint16) for _ in range(3))
+        rand_t = tuple(torch.from_numpy(r.view(np.int16).copy()).to(dev) for r in rand_np)
+    taps_t = tuple(torch.empty(n, dtype=torch.float32, device=dev) for _ in range(3)) if taps else (None,) * 3
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, seed=seed, tensor_id=tensor_id, index0=index0,
+                     rand=rand_t, taps=taps_t)
+    torch.cuda.synchronize()
+    f32 = oracle.adamw_sr(p, g, m, v, CODE[kp], CODE[kg], CODE[ks], ho, seed=seed, tensor_id=tensor_id,
+                          index0=index0, rand=rand_np, want_f32=True)
+    got = tuple(to_numpy(t) for t in (tp, tm, tv))
+    # guard elements around the views must be untouched
+    for big in (bp, bm, bv):
+        assert float(big[:misalign].float().abs().sum()) == 0
+        assert float(big[misalign + n:].float().abs().sum()) == 0
+    return got, (p, m, v), f32, tuple(None if t is None else t.cpu().numpy() for t in taps_t)
+
+
+SIZES = [1, 7, 8, 9, 255, 2048, 4099, 8192, 8193, 100003, (1 << 20) + 13]
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("kinds", [("bf16", "bf16", "bf16"), ("bf16", "bf16", "f32")])
+def test_production_kernel_is_bit_exact_with_checker(n, kinds):
+    got, want, _, _ = run_both(n, *kinds)
+    for a, b in zip(got, want):
+        assert bits_equal(a, b) == 0
+
+
+@pytest.mark.parametrize("kp", ["bf16", "f32", "f16"])
+@pytest.mark.parametrize("kg", ["bf16", "f32", "f16"])
+@pytest.mark.parametrize("ks", ["bf16", "f32", "f16"])
+def test_every_dtype_combination(kp, kg, ks):
+    got, want, _, _ = run_both(20011, kp, kg, ks, wd=0.0 if kp == "f16" else 0.01)
+    for a, b in zip(got, want):
+        assert bits_equal(a, b) == 0
+
+
+@pytest.mark.parametrize("misalign", [1, 3, 4])
+@pytest.mark.parametrize("kinds", [("bf16", "bf16", "bf16"), ("bf16", "f32", "f32")])
+def test_misaligned_views_take_the_scalar_path_with_identical_results(misalign, kinds):
+    got, want, _, _ = run_both(10007, *kinds, misalign=misalign)
+    for a, b in zip(got, want):
+        assert bits_equal(a, b) == 0
+
+
+def test_index0_offsets_select_the_same_draws_as_the_whole_tensor():
+    # a tensor updated in two slices (as the streaming path and ZeRO shards do) equals the
+    # tensor updated at once
+    n, cut = 50000, 16384
+    whole, _, _, _ = run_both(n, "bf16", "bf16", "bf16")
+    p, g, m, v = synth(n, "bf16", "bf16", "bf16", 0)
+    hn, _ = _hyper_pair()
+    dev = torch.device("cuda")
+    ts = [to_torch(a, "bf16", dev) for a in (p, g, m, v)]
+    for lo, hi in ((0, cut), (cut, n)):
+        F.adamw_sr_flat_(*(t[lo:hi] for t in ts), hn, seed=3, tensor_id=5, index0=lo)
+    torch.cuda.synchronize()
+    for a, t in zip(whole, (ts[0], ts[2], ts[3])):
+        assert bits_equal(a, to_numpy(t)) == 0
+
+
+@pytest.mark.parametrize("kinds", [("bf16", "bf16", "bf16"), ("bf16", "bf16", "f32"), ("f32", "f32", "f32")])
+def test_debug_kernel_taps_and_injected_draws(kinds):
+    n = 30001
+    got, want, f32_want, taps = run_both(n, *kinds, inject=True, taps=True)
+    # fp32 pre-rounding update: north-star tolerance 1e-6 relative; in fact identical bits
+    for a, b in zip(taps, f32_want):
+        assert bits_equal(a, b) == 0
+    # identical random bits -> bit-exact results
+    for a, b in zip(got, want):
+        assert bits_equal(a, b) == 0
+    # and the bf16 outputs are the integer map applied to the kernel's own fp32 values
+    p, g, m, v = synth(n, *kinds, 0)
+    if kinds[0] == "bf16":
+        rng = np.random.default_rng(99)
+        rp = rng.integers(0, 65536, n, dtype=np.uint16)
+        assert (oracle.sr_round_np(taps[0], rp) == got[0]).all()
+
+
+def test_debug_and_production_kernels_agree():
+    a, _, _, _ = run_both(12345, "bf16", "bf16", "bf16", taps=True)
+    b, _, _, _ = run_both(12345, "bf16", "bf16", "bf16")
+    for x, y in zip(a, b):
+        assert bits_equal(x, y) == 0
+
+
+@pytest.mark.parametrize("name", step_cases())
+def test_golden_steps_on_gpu(name):
+    """The reference's own recorded steps: same inputs, the reference's draws injected."""
+    d = load_golden(name)
+    meta = d["meta"]
+    if meta.get("centralization", 0):
+        pytest.skip("centralization is exercised through the optimizer class")
+    from ramtorch_b200 import _native as N
+    kp, kg, ks = meta["p_dtype"], meta["g_dtype"], meta["state_dtype"]
+    dev = torch.device("cuda")
+    tp, tg, tm, tv = (to_torch(d["in_" + k], kind, dev) for k, kind in zip("pgmv", (kp, kg, ks, ks)))
+    h = N.make_hyper(meta["lr"], tuple(meta["betas"]), meta["eps"], meta["weight_decay"], meta["step"])
+    rand = tuple(None if ("r16_" + k) not in d else torch.from_numpy(d["r16_" + k].view(np.int16).copy()).to(dev)
+                 for k in "pmv")
+    taps = tuple(torch.empty(tp.numel(), dtype=torch.float32, device=dev) for _ in range(3))
+    F.adamw_sr_flat_(tp, tg, tm, tv, h, rand=rand, taps=taps)
+    torch.cuda.synchronize()
+    # against the checker: identical
+    p, g, m, v = (d["in_" + k].copy() for k in "pgmv")
+    ho = oracle.make_hyper(meta["lr"], tuple(meta["betas"]), meta["eps"], meta["weight_decay"], meta["step"])
+    f32 = oracle.adamw_sr(p, g, m, v, CODE[kp], CODE[kg], CODE[ks], ho,
+                          rand=tuple(d.get("r16_" + k) for k in "pmv"), want_f32=True)
+    for t, want in zip((tp, tm, tv), (p, m, v)):
+        assert bits_equal(to_numpy(t), want) == 0
+    for t, want in zip(taps, f32):
+        assert bits_equal(t.cpu().numpy(), want) == 0
+    # against the reference's recorded fp32 values: 1e-6 relative, safe denominator
+    if "f32_p" in d:
+        old = oracle.bf16_bits_to_f32(d["in_p"]).astype(np.float64)
+        ref = d["f32_p"].astype(np.float64)
+        den = np.maximum(np.abs(old), np.abs(ref - old))
+        rel = np.abs(taps[0].cpu().numpy().astype(np.float64) - ref) / np.where(den > 0, den, 1)
+        assert rel.max() <= 1e-6
+    if "f32_m" in d:
+        assert bits_equal(taps[1].cpu().numpy(), d["f32_m"]) == 0
+        assert bits_equal(taps[2].cpu().numpy(), d["f32_v"]) == 0
+    # against the reference's final tensors: at most one bf16 step apart, almost all identical
+    for t, key in zip((tp, tm, tv), ("out_p", "out_m", "out_v")):
+        got, want = to_numpy(t), d[key]
+        if got.dtype == np.uint16:
+            diff = np.abs(got.astype(np.int64) - want.astype(np.int64))
+            assert diff.max() <= 1 and (diff != 0).mean() <= 2e-3
+
+
+@pytest.mark.parametrize("name", ["sr_edge.npz", "sr_random.npz"])
+def test_sr_round_golden_on_gpu(name):
+    d = load_golden(name)
+    dev = torch.device("cuda")
+    src = torch.from_numpy(d["source_bits"].astype(np.uint32).view(np.float32).copy()).to(dev)
+    r = torch.from_numpy(d["r16"].view(np.int16).copy()).to(dev)
+    out = torch.empty(src.numel(), dtype=torch.bfloat16, device=dev)
+    F.sr_round_bf16_(out, src, rand16=r)
+    got, want = to_numpy(out), d["target_bits"]
+    want_nan = (want & 0x7FFF) > 0x7F80
+    assert (((got & 0x7FFF) > 0x7F80) == want_nan).all()
+    assert (got[~want_nan] == want[~want_nan]).all()
+    assert (got == oracle.sr_round_bf16(src.cpu().numpy(), d["r16"])).all()
+
+
+@pytest.mark.parametrize("n", [1, 8, 1000, 65536 + 3])
+def test_sr_round_philox_stream_matches_checker(n):
+    dev = torch.device("cuda")
+    x = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(dev)
+    out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    F.sr_round_bf16_(out, x, seed=2**40 + 17, tensor_id=9, step=33, stream_id=2)
+    r = oracle.draws(2**40 + 17, 9, 33, 2, 0, n)
+    assert (to_numpy(out) == oracle.sr_round_bf16(x.cpu().numpy(), r)).all()
+
+
+def test_stochastic_rounding_is_unbiased_over_a_million_trials():
+    """out in {floor, ceil} of the fp32 value and the mean over 10^6 roundings within 3 sigma."""
+    dev = torch.device("cuda")
+    n = 1_000_000
+    for value in (1.00212, -0.0123456, 3.14159e-5):
+        x = torch.full((n,), value, dtype=torch.float32, device=dev)
+        out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        F.sr_round_bf16_(out, x, seed=1234, tensor_id=1, step=5)
+        o = out.float().cpu().numpy().astype(np.float64)
+        x32 = np.float32(value)
+        bits = np.array([x32]).view(np.uint32)[0]
+        lo = np.array([bits & 0xFFFF0000], np.uint32).view(np.float32)[0]
+        hi = np.array([(bits & 0xFFFF0000) + 0x10000], np.uint32).view(np.float32)[0]
+        assert set(np.unique(o)) <= {float(lo), float(hi)}
+        f = (bits & 0xFFFF) / 65536.0
+        ulp = abs(float(hi) - float(lo))
+        sigma = ulp * np.sqrt(f * (1 - f) / n)
+        assert abs(o.mean() - float(x32)) <= 3 * sigma + 1e-30
+
+
+def test_large_flat_tensor_spot_checked_against_checker():
+    """2^27 elements (fp32 moments, the roofline configuration's dtypes): whole-buffer
+    properties plus slices recomputed by the checker at their own index0."""
+    n = 1 << 27
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    p = (torch.randn(n, device=dev, generator=g) * 0.02).bfloat16()
+    gr = (torch.randn(n, device=dev, generator=g) * 1e-3).bfloat16()
+    m = torch.randn(n, device=dev, generator=g) * 1e-3
+    v = (torch.randn(n, device=dev, generator=g) * 1e-6).abs()
+    p0, m0, v0 = p.clone(), m.clone(), v.clone()
+    hn, ho = _hyper_pair(step=100)
+    F.adamw_sr_flat_(p, gr, m, v, hn, seed=7, tensor_id=0)
+    torch.cuda.synchronize()
+    # the update moved every parameter by at most lr * (1 + tiny) + decay, never produced NaN
+    assert torch.isfinite(p.float()).all() and torch.isfinite(m).all() and torch.isfinite(v).all()
+    assert float((p.float() - p0.float()).abs().max()) <= 2.5e-4 + 0.02 * 8 * 2 ** -8
+    for lo in (0, 8 * 12345, n // 2 + 64, n - 65536):
+        hi = lo + 65536
+        ps, gs, ms, vs = (to_numpy(t[lo:hi]) for t in (p0, gr, m0, v0))
+        oracle.adamw_sr(ps, gs, ms, vs, oracle.BF16, oracle.BF16, oracle.F32, ho, seed=7, tensor_id=0, index0=lo)
+        assert bits_equal(ps, to_numpy(p[lo:hi])) == 0
+        assert bits_equal(ms, to_numpy(m[lo:hi])) == 0
+        assert bits_equal(vs, to_numpy(v[lo:hi])) == 0

@@ -1,0 +1,214 @@
+"""GPU: the drop-in ``AdamW`` class against the CPU checker over several steps, on ragged
+multi-tensor lists, with HBM-resident and host-resident (streamed) parameters and moments."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from util import CODE, bits_equal, to_numpy
+
+pytestmark = pytest.mark.gpu
+KIND = {torch.bfloat16: "bf16", torch.float32: "f32", torch.float16: "f16"}
+
+
+def make_params(shapes, dtype, device, seed=0, pin=False):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for s in shapes:
+        t = (torch.randn(s, generator=g) * 0.02).to(dtype)
+        if device == "cpu":
+            t = t.pin_memory() if pin else t
+        else:
+            t = t.to(device)
+        out.append(t)
+    return out
+
+
+def make_grads(shapes, dtype, seed):
+    g = torch.Generator().manual_seed(1000 + seed)
+    return [(torch.randn(s, generator=g) * 1e-3).to(dtype) for s in shapes]
+
+
+class Mirror:
+    """The same optimisation carried out by the CPU checker, tensor by tensor."""
+
+    def __init__(self, params, state_dtype, seed, ids=None, **hp):
+        self.p = [to_numpy(p) for p in params]
+        self.kp = [KIND[p.dtype] for p in params]
+        self.ks = KIND[state_dtype]
+        sdt = np.uint16 if self.ks == "bf16" else (np.float32 if self.ks == "f32" else np.float16)
+        self.m = [np.zeros(p.size, sdt) for p in self.p]
+        self.v = [np.zeros(p.size, sdt) for p in self.p]
+        self.step = [0] * len(params)
+        self.seed, self.hp = seed, hp
+        self.ids = ids or list(range(len(params)))
+
+    def apply(self, grads, skip=()):
+        for k, g in enumerate(grads):
+            if k in skip:
+                continue
+            self.step[k] += 1
+            h = oracle.make_hyper(self.hp["lr"], self.hp["betas"], self.hp["eps"], self.hp["weight_decay"], self.step[k])
+            oracle.adamw_sr(self.p[k], to_numpy(g), self.m[k], self.v[k], CODE[self.kp[k]], CODE[KIND[g.dtype]],
+                            CODE[self.ks], h, seed=self.seed, tensor_id=self.ids[k])
+
+
+SHAPES = [(64,), (1000,), (37, 111), (8192,), (3, 5, 7), (1,), (20000,), (129, 64)]
+HP = dict(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+
+
+def check(opt, params, mirror):
+    for k, p in enumerate(params):
+        assert bits_equal(to_numpy(p), mirror.p[k]) == 0, f"param {k}"
+        st = opt.state[p]
+        assert st["step"] == mirror.step[k]
+        assert bits_equal(to_numpy(st["ema"]), mirror.m[k]) == 0, f"ema {k}"
+        assert bits_equal(to_numpy(st["ema_squared"]), mirror.v[k]) == 0, f"ema_squared {k}"
+        assert st["ema"].shape == p.shape and st["ema_squared"].shape == p.shape
+
+
+@pytest.mark.parametrize("state_dtype", [torch.bfloat16, torch.float32])
+def test_resident_multi_tensor_steps(state_dtype):
+    from ramtorch_b200 import AdamW
+    params = make_params(SHAPES, torch.bfloat16, "cuda")
+    opt = AdamW(params, dtype=state_dtype, storage_device="cuda", seed=11, **HP)
+    mirror = Mirror(params, state_dtype, 11, **HP)
+    for s in range(4):
+        grads = make_grads(SHAPES, torch.bfloat16, s)
+        skip = {2} if s == 1 else set()   # a parameter without a gradient is skipped, its step stays
+        for k, (p, g) in enumerate(zip(params, grads)):
+            p.grad = None if k in skip else g.cuda()
+        opt.step()
+        mirror.apply(grads, skip)
+        check(opt, params, mirror)
+    assert opt.last_step_info["launches"] == 1
+    assert opt.last_step_info["resident"] == len(SHAPES)
+
+
+def test_mixed_dtypes_use_one_launch_per_combination():
+    from ramtorch_b200 import AdamW
+    shapes = SHAPES[:6]
+    dts = [torch.bfloat16, torch.float32, torch.bfloat16, torch.float16, torch.float32, torch.bfloat16]
+    params = [make_params([s], dt, "cuda", seed=k)[0] for k, (s, dt) in enumerate(zip(shapes, dts))]
+    opt = AdamW(params, dtype=torch.float32, storage_device="cuda", **HP)
+    mirror = Mirror(params, torch.float32, 0, **HP)
+    for s in range(2):
+        grads = [make_grads([sh], dt, 10 * s + k)[0] for k, (sh, dt) in enumerate(zip(shapes, dts))]
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step()
+        mirror.apply(grads)
+        check(opt, params, mirror)
+    assert opt.last_step_info["launches"] == 3
+
+
+def test_param_groups_with_their_own_hyper_parameters_and_lr_schedule():
+    from ramtorch_b200 import AdamW
+    a = make_params(SHAPES[:3], torch.bfloat16, "cuda", seed=1)
+    b = make_params(SHAPES[3:6], torch.bfloat16, "cuda", seed=2)
+    opt = AdamW([{"params": a, "weight_decay": 0.0}, {"params": b, "lr": 3e-4}],
+                dtype=torch.bfloat16, storage_device="cuda", seed=5, **HP)
+    ma = Mirror(a, torch.bfloat16, 5, ids=[0, 1, 2], **{**HP, "weight_decay": 0.0})
+    mb = Mirror(b, torch.bfloat16, 5, ids=[3, 4, 5], **{**HP, "lr": 3e-4})
+    for s in range(3):
+        ga, gb = make_grads(SHAPES[:3], torch.bfloat16, s), make_grads(SHAPES[3:6], torch.bfloat16, 50 + s)
+        for p, g in zip(a + b, ga + gb):
+            p.grad = g.cuda()
+        # a scheduler mutates group["lr"] between steps (re-read every step, adamw.py:174)
+        opt.param_groups[1]["lr"] = 3e-4 * (0.5 ** s)
+        mb.hp["lr"] = 3e-4 * (0.5 ** s)
+        opt.step()
+        ma.apply(ga); mb.apply(gb)
+        check(opt, a, ma); check(opt, b, mb)
+
+
+def test_default_pinned_cpu_state_streams_and_matches_resident_state():
+    """storage_device="cpu" (the reference default): moments in pinned host RAM, parameters in
+    HBM.  Same seed -> bit-identical to the all-resident run."""
+    from ramtorch_b200 import AdamW
+    shapes = SHAPES + [(300001,)]
+    params = make_params(shapes, torch.bfloat16, "cuda")
+    opt = AdamW(params, **HP, seed=3, offload_chunk_elems=65536)   # dtype=bf16, storage_device="cpu"
+    assert all(opt.state[p]["ema"].is_pinned() and opt.state[p]["ema"].device.type == "cpu" for p in params)
+    mirror = Mirror(params, torch.bfloat16, 3, **HP)
+    for s in range(3):
+        grads = make_grads(shapes, torch.bfloat16, s)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step()
+        mirror.apply(grads)
+        check(opt, params, mirror)
+    assert opt.last_step_info["streamed"] == len(shapes)
+
+
+@pytest.mark.parametrize("pin", [True, False])
+def test_cpu_parameters_and_gradients_stream_through_the_gpu(pin):
+    """Parameters, gradients and moments all in host RAM (the ramtorch.Linear convention)."""
+    import warnings
+    from ramtorch_b200 import AdamW
+    shapes = [(1000,), (70001,), (64, 33), (200000,)]
+    params = make_params(shapes, torch.bfloat16, "cpu", pin=pin)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        opt = AdamW(params, dtype=torch.float32, **HP, seed=9, offload_chunk_elems=32768, offload_ring_depth=2)
+        mirror = Mirror(params, torch.float32, 9, **HP)
+        for s in range(3):
+            grads = make_grads(shapes, torch.bfloat16, s)
+            for p, g in zip(params, grads):
+                p.grad = g.pin_memory() if pin else g
+            opt.step()
+            mirror.apply(grads)
+            check(opt, params, mirror)
+
+
+def test_state_dict_round_trip_and_late_parameters():
+    from ramtorch_b200 import AdamW
+    params = make_params(SHAPES[:4], torch.bfloat16, "cuda")
+    opt = AdamW(params, dtype=torch.bfloat16, storage_device="cuda", **HP)
+    mirror = Mirror(params, torch.bfloat16, 0, **HP)
+    grads = make_grads(SHAPES[:4], torch.bfloat16, 0)
+    for p, g in zip(params, grads):
+        p.grad = g.cuda()
+    opt.step(); mirror.apply(grads)
+    sd = opt.state_dict()
+    assert set(sd["state"][0].keys()) == {"step", "ema", "ema_squared"}
+    opt2 = AdamW(params, dtype=torch.bfloat16, storage_device="cuda", **HP)
+    opt2.load_state_dict(sd)
+    grads = make_grads(SHAPES[:4], torch.bfloat16, 1)
+    for p, g in zip(params, grads):
+        p.grad = g.cuda()
+    opt2.step(); mirror.apply(grads)
+    check(opt2, params, mirror)
+    # a group added after construction gets its state lazily and the next free tensor id
+    late = make_params([(555,)], torch.bfloat16, "cuda", seed=77)
+    opt2.add_param_group({"params": late})
+    ml = Mirror(late, torch.bfloat16, 0, ids=[4], **HP)
+    gl = make_grads([(555,)], torch.bfloat16, 5)
+    for p in params:
+        p.grad = None
+    late[0].grad = gl[0].cuda()
+    opt2.step(); ml.apply(gl)
+    check(opt2, late, ml)
+
+
+def test_errors():
+    from ramtorch_b200 import AdamW
+    p = torch.zeros(16, dtype=torch.bfloat16, device="cuda")
+    opt = AdamW([p], storage_device="cuda")
+    p.grad = torch.sparse_coo_tensor(torch.tensor([[1]]), torch.tensor([1.0]), (16,), device="cuda").to(torch.bfloat16)
+    with pytest.raises(RuntimeError, match="sparse"):
+        opt.step()
+    q = torch.zeros(16, dtype=torch.float64, device="cuda")
+    opt = AdamW([q], storage_device="cuda")
+    q.grad = torch.zeros_like(q)
+    with pytest.raises(ValueError):
+        opt.step()
+
+
+def test_copy_stochastic_drop_in():
+    from ramtorch_b200 import copy_stochastic_
+    src = torch.randn(4097, device="cuda")
+    dst = torch.empty(4097, dtype=torch.bfloat16, device="cuda")
+    copy_stochastic_(dst, src, seed=53)
+    r = oracle.draws(53, 0, 0, 0, 0, 4097)
+    assert (to_numpy(dst) == oracle.sr_round_bf16(src.cpu().numpy(), r)).all()
