@@ -159,8 +159,10 @@ int rt_adamw_sr_multi(rt_plan* plan, const rt_hyper* hyper, int hyper_count,
 
 /*
  * Host-offloaded step (adamw.py:152-170, 204-222 when parameters and/or state live in CPU
- * RAM): streams one tensor through the GPU in chunks.  Each of p, g, m, v may be a pinned
- * host pointer or a device pointer; host-resident ones are staged through the ring of
+ * RAM): streams one tensor through the GPU in chunks.  Each of p, g, m, v may be a host
+ * pointer or a device pointer (pinned host memory overlaps its copies with the kernel;
+ * pageable host memory works but every copy is then synchronous); host-resident ones are
+ * staged through the ring of
  * device buffers in `staging` (at least ring_depth * chunk_elems * bytes-per-element of
  * the host-resident tensors).  H2D, kernel and D2H run on three library-owned side
  * streams, ordered by events; `cuda_stream` is made to wait for the pipeline's completion

@@ -59,14 +59,13 @@ static int get_pipe(int device, Pipe** out) {
 
 static int64_t round256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
-struct Residency { bool host; };
-
+// Where does a pointer live?  Pinned (or registered) host memory streams asynchronously; plain
+// pageable host memory is accepted too, but the runtime then stages every copy itself and
+// the copies no longer overlap (cudaMemcpyAsync is synchronous for pageable buffers).
 static int is_host_ptr(const void* ptr, bool* host) {
   cudaPointerAttributes a{};
   RT_CUDA(cudaPointerGetAttributes(&a, ptr));
-  if (a.type == cudaMemoryTypeUnregistered)
-    return fail(RT_E_CONFIG, "pageable host memory cannot be streamed: pin it (torch pin_memory or rt_host_register)");
-  *host = (a.type == cudaMemoryTypeHost);
+  *host = (a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeUnregistered);
   return 0;
 }
 

@@ -233,9 +233,20 @@ def test_large_flat_tensor_spot_checked_against_checker():
     hn, ho = _hyper_pair(step=100)
     F.adamw_sr_flat_(p, gr, m, v, hn, seed=7, tensor_id=0)
     torch.cuda.synchronize()
-    # the update moved every parameter by at most lr * (1 + tiny) + decay, never produced NaN
+    # whole-buffer check against a plain PyTorch fp32 evaluation of the same update: moments within
+    # fp32 rounding, parameters within one bf16 step of the unrounded value
     assert torch.isfinite(p.float()).all() and torch.isfinite(m).all() and torch.isfinite(v).all()
-    assert float((p.float() - p0.float()).abs().max()) <= 2.5e-4 + 0.02 * 8 * 2 ** -8
+    g32 = gr.float()
+    m_ref = m0 * 0.9 + g32 * (1 - 0.9)
+    v_ref = v0 * 0.999 + g32 * g32 * (1 - 0.999)
+    assert float(((m - m_ref).abs() / (m0.abs() + g32.abs() + 1e-30)).max()) <= 1e-6
+    assert float(((v - v_ref).abs() / (v0.abs() + g32 * g32 + 1e-30)).max()) <= 1e-6
+    ss = 1e-4 / (1 - 0.9 ** 100)
+    den = v.sqrt() / ((1 - 0.999 ** 100) ** 0.5) + 1e-8
+    p_ref = p0.float() * (1 - ss * 0.01) - ss * m / den
+    ulp = torch.maximum(p_ref.abs(), p.float().abs()) * 2.0 ** -7
+    assert bool(((p.float() - p_ref).abs() <= ulp + 1e-30).all())
+    del g32, m_ref, v_ref, den, p_ref, ulp
     for lo in (0, 8 * 12345, n // 2 + 64, n - 65536):
         hi = lo + 65536
         ps, gs, ms, vs = (to_numpy(t[lo:hi]) for t in (p0, gr, m0, v0))
