@@ -36,9 +36,9 @@ BYTES_PER_ELEM = 22            # read p2 g2 m4 v4, write p2 m4 v4
 HP = dict(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 START_STEP = 99                # the timed steps start at t = 100
 # DRAM bytes per element of the fused kernel (bf16 p/g, fp32 moments) measured with ncu
-# (dram__bytes_read.sum + dram__bytes_write.sum over one launch; see profiles/).  None until a
-# capture exists.
-NCU_DRAM_BYTES_PER_ELEM = None
+# (dram__bytes_read.sum + dram__bytes_write.sum over one launch of 2^27 elements, see profiles/);
+# traffic is proportional to the element count, so it is scaled to the launch timed here.
+NCU_DRAM_BYTES_PER_ELEM = 21.6
 FALLBACK_HBM_GBS = 6650.0
 
 
