@@ -158,6 +158,37 @@ int rt_adamw_sr_multi(rt_plan* plan, const rt_hyper* hyper, int hyper_count,
                       uint64_t seed, void* cuda_stream);
 
 /*
+ * Multi-tensor step for callers that must not allocate.  No counterpart in the reference.
+ *
+ * rt_plan_create keeps its tensor, chunk and hyper-parameter tables in memory it obtains from
+ * cudaMalloc.  Some hosts of this library cannot do that: a process that has handed all of
+ * its device memory to its own pool (a raw cudaMalloc then fails or fragments the pool), or
+ * code running in a phase where the CUDA allocator is off limits because it synchronises
+ * the device.  This entry point performs the same update as rt_plan_create +
+ * rt_adamw_sr_multi but keeps the tables in a fixed array that is part of the library image
+ * (about 595 KiB of device memory on every GPU that loads the library, until exit).  It
+ * calls no cudaMalloc, cudaFree, cudaHostAlloc or any other allocating routine; parameters,
+ * gradients and moments still come from the caller.
+ *
+ * Limits (larger requests are rejected with RT_E_SIZE and a message, nothing is launched):
+ *   count <= RT_STATIC_MAX_TENSORS, hyper_count <= RT_STATIC_MAX_HYPER,
+ *   sum over tensors of ceil(numel / 8192) <= RT_STATIC_MAX_CHUNKS (512 Mi elements when
+ *   every tensor is a multiple of 8192 long).
+ *
+ * The first call on a device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture.  All calls on a device
+ * share the one array: each call overwrites the part of the tables it uses (nothing needs
+ * to start at zero), so two calls whose GPU work can overlap -- different streams without an
+ * ordering between them -- race on it.  Calls on one stream are ordered and safe.
+ */
+#define RT_STATIC_MAX_TENSORS 1024
+#define RT_STATIC_MAX_CHUNKS 65536
+#define RT_STATIC_MAX_HYPER 64
+int rt_adamw_sr_multi_static(const rt_tensor_desc* tensors, int64_t count,
+                             const rt_hyper* hyper, int hyper_count, uint64_t seed,
+                             void* cuda_stream);
+
+/*
  * Host-offloaded step (adamw.py:152-170, 204-222 when parameters and/or state live in CPU
  * RAM): streams one tensor through the GPU in chunks.  Each of p, g, m, v may be a host
  * pointer or a device pointer (pinned host memory overlaps its copies with the kernel;

@@ -65,6 +65,8 @@ _SIGNATURES = {
     "rt_plan_set_grads": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_void_p]),
     "rt_plan_launches": (c_int, [c_void_p]),
     "rt_adamw_sr_multi": (c_int, [c_void_p, ctypes.POINTER(Hyper), c_int, c_uint64, c_void_p]),
+    "rt_adamw_sr_multi_static": (c_int, [ctypes.POINTER(TensorDesc), c_int64, ctypes.POINTER(Hyper), c_int,
+                                         c_uint64, c_void_p]),
     "rt_offload_staging_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "rt_adamw_sr_offload": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                     ctypes.POINTER(Hyper), c_uint64, c_uint32,
