@@ -10,6 +10,7 @@ Public surface (same names as the reference package, ramtorch/__init__.py:1-4 an
 The arithmetic runs in ``librt_b200.so`` (hand-written CUDA behind the C ABI declared in
 ``include/rt_b200.h``).  There is no CPU implementation.
 """
+from . import helpers, stochastic_optimizers, zero1, zero2
 from .stochastic_optimizers.adamw import AdamW, copy_stochastic_
 
 __all__ = ["AdamW", "copy_stochastic_"]

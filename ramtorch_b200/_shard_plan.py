@@ -1,0 +1,177 @@
+"""Flat layout shared by ZeRO-1 (parameter all-gather) and ZeRO-2 (gradient reduce-scatter).
+
+The reference moves one tensor per collective: a ``dist.broadcast`` per parameter after the step
+(ramtorch/zero1.py:78-91) and a ``dist.reduce`` per gradient during backward
+(ramtorch/zero2.py:27-57).  Here the parameters of every (device, dtype) are packed, grouped by
+owner rank, into one flat buffer
+
+    [ rank 0's tensors | pad ][ rank 1's tensors | pad ] ... [ rank W-1's tensors | pad ]
+
+with equal-length segments, and each parameter's ``.data`` becomes a view into it.  One in-place
+``all_gather_into_tensor`` then redistributes all updated parameters, and one in-place
+``reduce_scatter_tensor`` over an identically laid out gradient buffer delivers every owner the
+sum of its gradients.  Ownership stays at whole-tensor granularity, exactly as the dict returned
+by ``create_zero_param_groups`` says, so ``optimizer.state[p]`` and ``state_dict()`` keep the
+reference's shape.
+"""
+from __future__ import annotations
+
+import hashlib
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+ALIGN_BYTES = 256
+
+
+class Bucket:
+    """All flattened parameters of one (device, dtype)."""
+
+    def __init__(self, device, dtype, world_size):
+        self.device, self.dtype, self.world_size = device, dtype, world_size
+        self.params: List[torch.Tensor] = []
+        self.owner: List[int] = []
+        self.offset: List[int] = []          # element offset of each parameter inside `flat`
+        self.segment = 0                     # elements per rank segment
+        self.flat: Optional[torch.Tensor] = None
+        self.gflat: Optional[torch.Tensor] = None
+        self.grad_views: List[Optional[torch.Tensor]] = []
+        self.ready = 0                       # gradients accumulated since the last reduction
+        self.expected = 0                    # parameters that take part in backward
+
+    def rank_segment(self, buf: torch.Tensor, rank: int) -> torch.Tensor:
+        return buf[rank * self.segment:(rank + 1) * self.segment]
+
+
+class ShardPlan:
+    def __init__(self, rank_param_groups: Dict[int, list]):
+        self.world_size = len(rank_param_groups)
+        if sorted(rank_param_groups) != list(range(self.world_size)):
+            raise ValueError("rank_param_groups must have one entry per rank 0..world_size-1")
+        self.buckets: Dict[tuple, Bucket] = {}
+        self.loose: List[tuple] = []         # (param, owner): redistributed one tensor at a time
+        self.ramtorch: List[tuple] = []      # CPU-shared parameters: nothing to redistribute
+        self.owner_of: Dict[int, int] = {}       # id(param) -> owner rank
+        self.bucket_of: Dict[int, tuple] = {}    # id(param) -> bucket key
+        self.current_rank: Optional[int] = None
+        self.flattened = False
+        self.verified = False
+        seen = set()
+        per_owner: Dict[tuple, Dict[int, list]] = {}
+        # same iteration order as the reference (zero1.py:78-80, zero2.py:18-21): it is what keeps
+        # the collectives matched across ranks
+        for owner in range(self.world_size):
+            for group in rank_param_groups[owner]:
+                for p in group["params"]:
+                    self.owner_of[id(p)] = owner
+                    if id(p) in seen:
+                        continue
+                    seen.add(id(p))
+                    if getattr(p, "is_ramtorch", False):
+                        self.ramtorch.append((p, owner))
+                    elif not p.data.is_contiguous():
+                        self.loose.append((p, owner))
+                    else:
+                        key = (p.device, p.dtype)
+                        per_owner.setdefault(key, {}).setdefault(owner, []).append(p)
+        for key, owners in per_owner.items():
+            b = Bucket(key[0], key[1], self.world_size)
+            align = max(1, ALIGN_BYTES // torch.empty((), dtype=key[1]).element_size())
+            rel, longest = {}, 0
+            for owner in range(self.world_size):
+                cur = 0
+                for p in owners.get(owner, []):
+                    rel[id(p)] = cur
+                    cur += (p.numel() + align - 1) // align * align
+                longest = max(longest, cur)
+            b.segment = max(longest, align)
+            for owner in range(self.world_size):
+                for p in owners.get(owner, []):
+                    b.params.append(p)
+                    b.owner.append(owner)
+                    b.offset.append(owner * b.segment + rel[id(p)])
+                    self.bucket_of[id(p)] = key
+            self.buckets[key] = b
+
+    # ------------------------------------------------------------------ layout identity
+    def fingerprint(self) -> str:
+        h = hashlib.sha256()
+        h.update(str(self.world_size).encode())
+        for key in sorted(self.buckets, key=str):
+            b = self.buckets[key]
+            h.update(f"|{key[0].type}:{key[1]}:{b.segment}".encode())
+            for p, o, off in zip(b.params, b.owner, b.offset):
+                h.update(f";{tuple(p.shape)}@{o}+{off}".encode())
+        for p, o in self.loose:
+            h.update(f"|loose{tuple(p.shape)}{p.dtype}@{o}".encode())
+        return h.hexdigest()
+
+    def verify_across_ranks(self) -> None:
+        """Every rank must have built the same layout, or the flat collectives would silently mix
+        tensors.  Compared once, on the host, before any data-path collective."""
+        if self.verified or not (dist.is_available() and dist.is_initialized()):
+            return
+        if dist.get_world_size() != self.world_size:
+            raise ValueError(f"rank_param_groups describes {self.world_size} ranks but the process group "
+                             f"has {dist.get_world_size()}")
+        mine = self.fingerprint()
+        everyone = [None] * self.world_size
+        dist.all_gather_object(everyone, mine)
+        if any(f != mine for f in everyone):
+            bad = [r for r, f in enumerate(everyone) if f != everyone[0]]
+            raise RuntimeError(f"ZeRO shard plans differ between ranks (ranks {bad} disagree with rank 0): "
+                               "parameter order, shapes or dtypes are not identical everywhere")
+        self.verified = True
+
+    # ------------------------------------------------------------------ flattening
+    def flatten_params(self) -> None:
+        """Move every bucket's parameters into its flat buffer and re-point ``p.data`` at the views."""
+        if self.flattened:
+            return
+        with torch.no_grad():
+            for b in self.buckets.values():
+                b.flat = torch.zeros(b.segment * self.world_size, dtype=b.dtype, device=b.device)
+                for p, off in zip(b.params, b.offset):
+                    view = b.flat[off:off + p.numel()].view(p.shape)
+                    view.copy_(p.data)
+                    p.data = view
+        self.flattened = True
+
+    def attach_grad_buffers(self) -> None:
+        """Allocate the flat gradient buffers and make every ``p.grad`` a view so that autograd
+        accumulates straight into them."""
+        for b in self.buckets.values():
+            if b.gflat is not None:
+                continue
+            b.gflat = torch.zeros(b.segment * self.world_size, dtype=b.dtype, device=b.device)
+            b.grad_views = []
+            b.expected = 0
+            for p, off in zip(b.params, b.offset):
+                if p.requires_grad:
+                    view = b.gflat[off:off + p.numel()].view(p.shape)
+                    b.grad_views.append(view)
+                    p.grad = view
+                    b.expected += 1
+                else:
+                    b.grad_views.append(None)
+
+
+_PLANS: Dict[int, tuple] = {}
+
+
+def plan_for(rank_param_groups) -> ShardPlan:
+    """The plan attached to a ``rank -> groups`` dict (built on first use).  Hand-built dicts work
+    too: the plan is cached by object identity and the dict is kept alive with it."""
+    plan = getattr(rank_param_groups, "plan", None)
+    if plan is not None:
+        return plan
+    hit = _PLANS.get(id(rank_param_groups))
+    if hit is not None and hit[0] is rank_param_groups:
+        return hit[1]
+    plan = ShardPlan(rank_param_groups)
+    try:
+        rank_param_groups.plan = plan
+    except AttributeError:
+        _PLANS[id(rank_param_groups)] = (rank_param_groups, plan)
+    return plan

@@ -1,0 +1,51 @@
+"""Hook-dict protocol used by ZeRO-2 for CPU-resident (``is_ramtorch``) parameters.
+
+Only the two-attribute protocol of the reference (ramtorch/helpers.py:8-50) that
+``zero2.setup_grad_sharding_hooks`` relies on and that the reference's ``Linear`` backward consumes
+(ramtorch/modules/linear.py:76-94): a tensor carries ``<name>`` (an ``OrderedDict`` id -> callable)
+and ``<name>_counter`` (next id).  The model-surgery helpers of that file are not part of this
+package.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Callable
+
+import torch
+
+ZERO2_HOOK_NAME = "_ramtorch_zero_2_hooks"
+
+
+def add_custom_hooks(tensor: torch.Tensor, hook_name: str = "_custom_hooks") -> torch.Tensor:
+    """Give ``tensor`` an empty hook dict and its id counter unless it has them already."""
+    if not hasattr(tensor, hook_name):
+        setattr(tensor, hook_name, OrderedDict())
+        setattr(tensor, hook_name + "_counter", 0)
+    return tensor
+
+
+def register_ramtorch_hook(tensor: torch.Tensor, hook: Callable, hook_name: str) -> int:
+    """Append ``hook`` to the tensor's hook dict ``hook_name``; returns the integer id under which
+    it was stored (ids are never reused)."""
+    add_custom_hooks(tensor, hook_name)
+    counter_name = hook_name + "_counter"
+    hook_id = getattr(tensor, counter_name)
+    getattr(tensor, hook_name)[hook_id] = hook
+    setattr(tensor, counter_name, hook_id + 1)
+    return hook_id
+
+
+def remove_ramtorch_hook(tensor: torch.Tensor, hook_id: int, hook_name: str) -> bool:
+    """Remove a hook by id; returns whether it was present."""
+    hooks = getattr(tensor, hook_name, None)
+    return hooks is not None and hooks.pop(hook_id, None) is not None
+
+
+def invoke_ramtorch_hooks(tensor: torch.Tensor, grad: torch.Tensor, hook_name: str = ZERO2_HOOK_NAME):
+    """Run the hook dict the way the reference's backward does (linear.py:76-94): every hook sees the
+    current gradient, a non-``None`` result replaces it."""
+    for hook in getattr(tensor, hook_name, {}).values():
+        out = hook(grad)
+        if out is not None:
+            grad = out
+    return grad

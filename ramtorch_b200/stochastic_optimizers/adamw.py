@@ -185,6 +185,8 @@ class AdamW(Optimizer):
             raise RuntimeError("ramtorch_b200.AdamW needs a CUDA device: there is no CPU fallback")
         lib = N.lib()
         self._keepalive.clear()
+        from ..zero2 import finish_grad_sync
+        finish_grad_sync()   # ZeRO-2: reduce buckets a partial backward left behind (no-op otherwise)
 
         resident = {}   # device index -> list of (p, grad, ema, ema_sq, tensor_id, hyper_index)
         streamed = []   # (device index, p, grad, ema, ema_sq, tensor_id, hyper_index)

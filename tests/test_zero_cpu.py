@@ -1,0 +1,192 @@
+"""CPU: the ZeRO-1 / ZeRO-2 host logic on gloo ranks (world_size 2 and 3) and against the ownership
+maps recorded from the reference.  No GPU and no optimizer kernel involved: the "optimizer" here
+is a plain in-place edit of the parameters a rank owns."""
+import json
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ramtorch_b200 import helpers
+from ramtorch_b200._shard_plan import ShardPlan, plan_for
+from ramtorch_b200.zero1 import PARAM_IDS_KEY, broadcast_zero_params, create_zero_param_groups
+from ramtorch_b200.zero2 import setup_grad_sharding_hooks
+from util import GOLDEN
+
+
+def test_ownership_matches_the_reference_fixtures():
+    with open(os.path.join(GOLDEN, "zero1_ownership.json")) as f:
+        cases = json.load(f)
+    for c in cases:
+        groups, k = [], 0
+        for gi, n in enumerate(c["group_sizes"]):
+            params = [torch.zeros(1) for _ in range(n)]
+            for t in params:
+                t.tag = k
+                k += 1
+            groups.append({"params": params, "lr": 0.1 * (gi + 1), "foo": f"g{gi}"})
+        rpg = create_zero_param_groups(groups, c["world_size"])
+        assert sorted(rpg) == list(range(c["world_size"]))
+        for r, gl in rpg.items():
+            assert [[p.tag for p in g["params"]] for g in gl] == c["ownership"][str(r)]
+            for g, extra in zip(gl, c["extra_keys"][str(r)]):
+                assert {k2: v for k2, v in g.items() if k2 not in ("params", PARAM_IDS_KEY)} == extra
+                # ids are the global positions, so they equal the tags assigned above
+                assert g[PARAM_IDS_KEY] == [p.tag for p in g["params"]]
+        # references, not copies
+        assert rpg[0][0]["params"][0] is groups[0]["params"][0] if c["group_sizes"][0] else True
+
+
+def test_flat_layout_is_owner_ordered_equal_segments_and_keeps_values():
+    params = [torch.arange(n, dtype=torch.float32) + 100 * k for k, n in enumerate([5, 300, 7, 64, 1])]
+    before = [p.clone() for p in params]
+    rpg = create_zero_param_groups([{"params": params}], 2)
+    plan = plan_for(rpg)
+    assert plan is plan_for(rpg)
+    (bucket,) = plan.buckets.values()
+    assert bucket.segment % 64 == 0 and bucket.segment >= 5 + 7 + 1
+    plan.flatten_params()
+    for p, b, owner, off in zip(bucket.params, [before[0], before[2], before[4], before[1], before[3]],
+                                bucket.owner, bucket.offset):
+        assert torch.equal(p, b)
+        assert owner * bucket.segment <= off < (owner + 1) * bucket.segment
+        assert off % 64 == 0
+        assert p.data_ptr() == bucket.flat.data_ptr() + 4 * off
+    # a hand-built plain dict works too
+    plain = {0: [{"params": [torch.ones(3)]}], 1: [{"params": [torch.ones(4)]}]}
+    assert isinstance(plan_for(plain), ShardPlan) and plan_for(plain) is plan_for(plain)
+
+
+def test_hook_dict_protocol():
+    t = torch.zeros(2)
+    a = helpers.register_ramtorch_hook(t, lambda g: g * 2, "_ramtorch_zero_2_hooks")
+    b = helpers.register_ramtorch_hook(t, lambda g: None, "_ramtorch_zero_2_hooks")
+    assert (a, b) == (0, 1) and t._ramtorch_zero_2_hooks_counter == 2
+    assert list(t._ramtorch_zero_2_hooks) == [0, 1]
+    assert torch.equal(helpers.invoke_ramtorch_hooks(t, torch.ones(2)), torch.full((2,), 2.0))
+    assert helpers.remove_ramtorch_hook(t, 0, "_ramtorch_zero_2_hooks")
+    assert helpers.register_ramtorch_hook(t, lambda g: g, "_ramtorch_zero_2_hooks") == 2
+
+
+# ------------------------------------------------------------------------------------------
+# multi-process part
+# ------------------------------------------------------------------------------------------
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _model(seed=0):
+    torch.manual_seed(seed)
+    return torch.nn.Sequential(torch.nn.Linear(13, 32), torch.nn.Tanh(), torch.nn.Linear(32, 7, bias=False),
+                               torch.nn.Tanh(), torch.nn.Linear(7, 3))
+
+
+def _worker(rank, world, port, scenario, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        result = SCENARIOS[scenario](rank, world)
+        out.put((rank, "ok", result))
+    except Exception as e:  # report instead of hanging the other ranks' collectives
+        out.put((rank, "error", f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(scenario, world):
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, scenario, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get() for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    return sorted(results)
+
+
+def _scenario_full_loop(rank, world):
+    """ZeRO-2 reduce + owner-only update + ZeRO-1 redistribution over two steps with gradient
+    accumulation, compared with a single-process run on the summed gradients."""
+    model, ref = _model(), _model()
+    groups = [{"params": [p for n, p in model.named_parameters() if n.endswith("bias")], "tag": "b"},
+              {"params": [p for n, p in model.named_parameters() if n.endswith("weight")], "tag": "w"}]
+    rpg = create_zero_param_groups(groups, world)
+    handles = setup_grad_sharding_hooks(rpg, rank)
+    assert len(handles) == sum(len(g["params"]) for g in groups)
+    mine = [p for g in rpg[rank] for p in g["params"]]
+    for step in range(2):
+        for micro in range(2):                   # gradient accumulation: two backward passes
+            for r in range(world):               # the reference run sees every rank's batch
+                x = torch.randn(4, 13, generator=torch.Generator().manual_seed(100 * step + 10 * micro + r))
+                if r == rank:
+                    model(x).square().sum().backward()
+                ref(x).square().sum().backward()
+        from ramtorch_b200.zero2 import finish_grad_sync
+        finish_grad_sync()
+        # owner's gradient = SUM over ranks (and over micro-batches)
+        ref_params = dict(ref.named_parameters())
+        for n, p in model.named_parameters():
+            if any(p is q for q in mine):
+                assert torch.allclose(p.grad, ref_params[n].grad, rtol=1e-5, atol=1e-6), n
+        with torch.no_grad():
+            for p in mine:                       # stand-in optimizer: owners update their tensors
+                p.data.sub_(0.1 * p.grad)
+            for p in ref.parameters():
+                p.sub_(0.1 * p.grad)
+        assert broadcast_zero_params(rpg) is None
+        for (n, p), q in zip(model.named_parameters(), ref.parameters()):
+            assert torch.allclose(p, q, rtol=1e-5, atol=1e-6), n
+        if step == 0:
+            model.zero_grad(set_to_none=True)    # drops the flat views; the hooks fold them back
+        else:
+            model.zero_grad(set_to_none=False)
+        ref.zero_grad()
+    return True
+
+
+def _scenario_plan_mismatch(rank, world):
+    """A rank whose parameter list differs must be caught on the host before any data collective."""
+    params = [torch.zeros(4), torch.zeros(6 if rank == 0 else 8)]
+    rpg = create_zero_param_groups([{"params": params}], world)
+    try:
+        broadcast_zero_params(rpg)
+    except RuntimeError as e:
+        return "differ" in str(e)
+    return False
+
+
+def _scenario_ramtorch_hooks(rank, world):
+    """CPU-shared parameters keep the hook-dict protocol and the per-tensor synchronous reduce."""
+    w = torch.nn.Parameter(torch.zeros(5))
+    w.is_ramtorch = True
+    plain = torch.nn.Parameter(torch.ones(3) * (rank + 1))
+    rpg = create_zero_param_groups([{"params": [w, plain]}], world)
+    handles = setup_grad_sharding_hooks(rpg, rank)
+    assert isinstance(handles[0], int) and hasattr(w, "_ramtorch_zero_2_hooks")
+    grad = torch.full((5,), float(rank + 1))
+    out = helpers.invoke_ramtorch_hooks(w, grad)
+    total = float(sum(range(1, world + 1)))
+    owner_ok = (rank != 0) or bool((out == total).all())
+    broadcast_zero_params(rpg)                   # skips w, redistributes `plain` from rank 1
+    return owner_ok and bool((plain == 2.0).all()) and bool((w == 0).all())
+
+
+SCENARIOS = {"full_loop": _scenario_full_loop, "plan_mismatch": _scenario_plan_mismatch,
+             "ramtorch_hooks": _scenario_ramtorch_hooks}
+
+
+@pytest.mark.parametrize("scenario,world", [("full_loop", 2), ("full_loop", 3), ("plan_mismatch", 2),
+                                            ("ramtorch_hooks", 2)])
+def test_gloo_ranks(scenario, world):
+    results = _spawn(scenario, world)
+    assert len(results) == world
+    for rank, status, payload in results:
+        assert status == "ok", f"rank {rank}: {payload}"
+        assert payload is True, f"rank {rank} returned {payload}"
