@@ -219,21 +219,28 @@ def main():
     warmup = max(args.warmup, 3)
 
     # ---------------------------------------------------------------- resident step (value)
-    flat = torch.empty(n * world, dtype=torch.bfloat16, device=device)   # the replicated parameters
-    shard = flat[rank * n:(rank + 1) * n]
+    # ZeRO-1 layout: one 2^30-element parameter per rank in one group, so the reference's round-robin
+    # (parameter k -> rank k % world) makes rank r the owner of parameter r.  Only the owned
+    # parameter has a gradient and moments on this rank.
+    from ramtorch_b200.zero1 import broadcast_zero_params, create_zero_param_groups
+    params = [torch.empty(n, dtype=torch.bfloat16, device=device) for _ in range(world)]
+    rpg = create_zero_param_groups([{"params": params}], world)
+    shard = params[rank]
     p0, grad, m0, v0 = synth_on_device(n, device, seed=rank)
     shard.copy_(p0)
     del p0
-    opt = AdamW([shard], dtype=torch.float32, storage_device=device, seed=0, sync=False, **HP)
+    opt = AdamW(rpg[rank], dtype=torch.float32, storage_device=device, seed=0, sync=False, **HP)
     st = opt.state[shard]
     st["ema"].copy_(m0); st["ema_squared"].copy_(v0); st["step"] = START_STEP
     del m0, v0
     shard.grad = grad
+    if world > 1:
+        broadcast_zero_params(rpg)   # builds the flat buffer and re-points the parameters into it
 
     def one_step():
         opt.step()
         if world > 1:
-            dist.all_gather_into_tensor(flat, shard)
+            broadcast_zero_params(rpg)
 
     for _ in range(warmup):
         one_step()
@@ -250,7 +257,7 @@ def main():
         opt.step()
         ev[3 * k + 1].record()
         if world > 1:
-            dist.all_gather_into_tensor(flat, shard)
+            broadcast_zero_params(rpg)
         ev[3 * k + 2].record()
         ev[3 * k + 3].record()
     torch.cuda.synchronize()
@@ -285,7 +292,7 @@ def main():
     if not args.no_e2e:
         del opt, st
         shard.grad = None
-        del grad, flat, shard
+        del grad, shard, params, rpg
         torch.cuda.empty_cache()
         n_host = n
         budget = host_mem_available_bytes() // max(world, 1)

@@ -1,0 +1,99 @@
+"""GPU (needs >= 2 devices): the whole ZeRO loop — flat reduce-scatter of gradients, owner-only fused
+SR-AdamW step, flat all-gather of parameters — on NCCL ranks, against a single-process run of the
+same optimizer on the summed gradients.  With the same seed the parameters must come out
+bit-identical whatever the world size (the random bits are keyed by global parameter id)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(257, 64), (64,), (1000, 33), (33,), (4096,), (8, 8, 8), (70001,), (5,), (129, 128)]
+HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+STEPS = 3
+
+
+def _params(device):
+    g = torch.Generator().manual_seed(0)
+    return [torch.nn.Parameter((torch.randn(s, generator=g) * 0.02).bfloat16().to(device)) for s in SHAPES]
+
+
+def _grad(step, rank, k, shape):
+    g = torch.Generator().manual_seed(1000 * step + 10 * rank + k)
+    # multiples of 2^-14 with few significant bits: sums of up to 8 ranks are exact in bf16, so the
+    # order in which NCCL adds them cannot matter
+    return (torch.randint(-8, 9, shape, generator=g).float() * 2.0 ** -14).bfloat16()
+
+
+def _groups(params):
+    return [{"params": [p for p in params if p.dim() == 1], "weight_decay": 0.0},
+            {"params": [p for p in params if p.dim() > 1]}]
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from ramtorch_b200 import AdamW
+        from ramtorch_b200.zero1 import broadcast_zero_params, create_zero_param_groups
+        from ramtorch_b200.zero2 import setup_grad_sharding_hooks
+        params = _params(dev)
+        rpg = create_zero_param_groups(_groups(params), world)
+        setup_grad_sharding_hooks(rpg, rank)
+        opt = AdamW(rpg[rank], dtype=torch.bfloat16, storage_device=dev, seed=21, **HP)
+        for step in range(STEPS):
+            # a "backward": every parameter receives this rank's gradient through autograd
+            loss = sum((p * _grad(step, rank, k, p.shape).to(dev)).sum() for k, p in enumerate(params))
+            loss.backward()
+            opt.step()
+            broadcast_zero_params(rpg)
+            for p in params:
+                p.grad = None if step % 2 == 0 else p.grad.zero_()
+        torch.cuda.synchronize()
+        out.put((rank, "ok", [p.detach().float().cpu() for p in params]))
+    except Exception as e:
+        import traceback
+        out.put((rank, "error", traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _single_process(world):
+    from ramtorch_b200 import AdamW
+    dev = torch.device("cuda", 0)
+    params = _params(dev)
+    opt = AdamW(_groups(params), dtype=torch.bfloat16, storage_device=dev, seed=21, **HP)
+    for step in range(STEPS):
+        for k, p in enumerate(params):
+            total = sum(_grad(step, r, k, p.shape).float() for r in range(world))
+            p.grad = total.bfloat16().to(dev)
+        opt.step()
+    return [p.detach().float().cpu() for p in params]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_zero_loop_matches_single_process(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((out.get() for _ in procs), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=120)
+    want = _single_process(world)
+    for rank, status, payload in results:
+        assert status == "ok", f"rank {rank}: {payload}"
+        for k, (a, b) in enumerate(zip(payload, want)):
+            assert torch.equal(a, b), f"rank {rank} parameter {k} differs from the single-process run"
