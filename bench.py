@@ -160,14 +160,15 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def synth_on_device(n, device, seed):
+def synth_on_device(n, device, seed, state_dtype=None):
     import torch
+    state_dtype = state_dtype or torch.float32
     g = torch.Generator(device=device).manual_seed(seed)
     blk = 1 << 28
     p = torch.empty(n, dtype=torch.bfloat16, device=device)
     grad = torch.empty(n, dtype=torch.bfloat16, device=device)
-    m = torch.empty(n, dtype=torch.float32, device=device)
-    v = torch.empty(n, dtype=torch.float32, device=device)
+    m = torch.empty(n, dtype=state_dtype, device=device)
+    v = torch.empty(n, dtype=state_dtype, device=device)
     for lo in range(0, n, blk):
         hi = min(n, lo + blk)
         p[lo:hi] = torch.randn(hi - lo, device=device, generator=g) * 0.02
@@ -188,14 +189,45 @@ def host_mem_available_bytes():
     return 0
 
 
+def llama_shapes():
+    """The 291 weight tensors of a 32-layer Llama-style decoder (hidden 4096, MLP 11008, vocab
+    32000) in module order: embedding, then per layer q k v o gate up down and two norms, the final
+    norm, the output head.  6,738,415,616 elements."""
+    shapes = [(32000, 4096)]
+    for _ in range(32):
+        shapes += [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)] + [(4096,)] * 2
+    shapes += [(4096,), (32000, 4096)]
+    return shapes
+
+
+def ragged_shapes(count=20000, lo=64, hi=4194304, seed=0):
+    """Sizes log-uniform in [lo, hi]; 1-D below 16384 elements, otherwise (size // 1024, 1024)
+    rounded down (2-D weights)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    sizes = np.floor(np.exp(rng.uniform(np.log(lo), np.log(hi), count))).astype(np.int64)
+    return [(int(s),) if s < 16384 else (int(s) // 1024, 1024) for s in sizes]
+
+
+WORKLOADS = {
+    "c2": "config 2: one 2^30-element bf16 parameter shard per GPU, fp32 moments, bf16 grads ~N(0,1e-3), t=100",
+    "bf16": "2^30-element bf16 parameter shard per GPU, bf16 moments (14 B/element), t=100",
+    "c1": "config 1: 16,777,216-element bf16 parameter, bf16 moments, t=11, rotating over 12 buffer sets",
+    "c3": "config 3: Llama-style 32-layer decoder shapes (291 tensors, 6.74e9 elements), bf16 moments, ZeRO-1",
+    "c5": "config 5: 20,000 ragged bf16 tensors, sizes log-uniform in [64, 4194304], bf16 moments, ZeRO-1",
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--elems", type=int, default=ELEMS_PER_GPU, help="elements per GPU (default 2^30)")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--elems", type=int, default=ELEMS_PER_GPU, help="elements per GPU for c2/bf16 (default 2^30)")
     ap.add_argument("--e2e-steps", type=int, default=4)
+    ap.add_argument("--fast-math", action="store_true", help="approximate sqrt/reciprocal in p' (off by default)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -205,6 +237,7 @@ def main():
     import torch
     import torch.distributed as dist
     from ramtorch_b200 import AdamW, _native as N
+    from ramtorch_b200.zero1 import broadcast_zero_params, create_zero_param_groups
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -215,84 +248,111 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    n = args.elems
     warmup = max(args.warmup, 3)
+    wl = args.workload
+    state_dtype = torch.float32 if wl == "c2" else torch.bfloat16
+    bytes_per_elem = 22 if wl == "c2" else 14
+    start_step = 10 if wl == "c1" else START_STEP
 
     # ---------------------------------------------------------------- resident step (value)
-    # ZeRO-1 layout: one 2^30-element parameter per rank in one group, so the reference's round-robin
-    # (parameter k -> rank k % world) makes rank r the owner of parameter r.  Only the owned
-    # parameter has a gradient and moments on this rank.
-    from ramtorch_b200.zero1 import broadcast_zero_params, create_zero_param_groups
-    params = [torch.empty(n, dtype=torch.bfloat16, device=device) for _ in range(world)]
-    rpg = create_zero_param_groups([{"params": params}], world)
-    shard = params[rank]
-    p0, grad, m0, v0 = synth_on_device(n, device, seed=rank)
-    shard.copy_(p0)
-    del p0
-    opt = AdamW(rpg[rank], dtype=torch.float32, storage_device=device, seed=0, sync=False, **HP)
-    st = opt.state[shard]
-    st["ema"].copy_(m0); st["ema_squared"].copy_(v0); st["step"] = START_STEP
-    del m0, v0
-    shard.grad = grad
-    if world > 1:
-        broadcast_zero_params(rpg)   # builds the flat buffer and re-points the parameters into it
+    # Every workload is a list of parameters in ONE group handed to create_zero_param_groups, so
+    # the reference's round-robin (parameter k -> rank k % world) decides ownership.  A rank
+    # holds all parameters (they are replicated) but gradients and moments only for the ones it owns.
+    steppers, rpgs = [], []
 
-    def one_step():
-        opt.step()
+    def make_set(shapes, seed):
+        params = [torch.empty(s, dtype=torch.bfloat16, device=device).normal_(0, 0.02) for s in shapes]
+        rpg = create_zero_param_groups([{"params": params}], world)
+        owned = rpg[rank][0]["params"]
+        opt = AdamW(rpg[rank], dtype=state_dtype, storage_device=device, seed=seed, sync=False,
+                    fast_math=args.fast_math, **HP)
+        for p in owned:
+            p.grad = torch.empty_like(p).normal_(0, 1e-3)
+            st = opt.state[p]
+            st["ema"].normal_(0, 1e-3)
+            st["ema_squared"].normal_(0, 1e-6).abs_()
+            st["step"] = start_step
         if world > 1:
-            broadcast_zero_params(rpg)
+            broadcast_zero_params(rpg)   # builds the flat buffer and re-points the parameters into it
+        rpgs.append(rpg)
+        steppers.append(opt)
+        return sum(p.numel() for p in owned)
 
-    for _ in range(warmup):
-        one_step()
+    if wl in ("c2", "bf16"):
+        # one shard per rank: `world` equal tensors, rank r owns tensor r
+        owned_elems = make_set([(args.elems,)] * world, 0)
+    elif wl == "c1":
+        owned_elems = [make_set([(1 << 24,)] * world, k) for k in range(12)][0]
+    elif wl == "c3":
+        owned_elems = make_set(llama_shapes(), 0)
+    else:
+        owned_elems = make_set(ragged_shapes(), 0)
+    torch.cuda.synchronize()
+
+    def one_step(k):
+        steppers[k % len(steppers)].step()
+
+    def redistribute(k):
+        if world > 1:
+            broadcast_zero_params(rpgs[k % len(rpgs)])
+
+    for k in range(max(warmup, len(steppers))):
+        one_step(k); redistribute(k)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     launches0 = N.stats()["kernel_launches"]
     t_wall0 = time.time()
     ev[0].record()
     for k in range(args.steps):
-        opt.step()
-        ev[3 * k + 1].record()
-        if world > 1:
-            broadcast_zero_params(rpg)
-        ev[3 * k + 2].record()
-        ev[3 * k + 3].record()
+        one_step(k)
+        ev[2 * k + 1].record()
+        redistribute(k)
+        ev[2 * k + 2].record()
+    host_ms = (time.time() - t_wall0) * 1e3 / args.steps
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     t_wall1 = time.time()
     launches = N.stats()["kernel_launches"] - launches0
-    total_ms = ev[0].elapsed_time(ev[3 * args.steps])
-    upd_ms = sum(ev[3 * k].elapsed_time(ev[3 * k + 1]) for k in range(args.steps)) / args.steps
-    ag_ms = sum(ev[3 * k + 1].elapsed_time(ev[3 * k + 2]) for k in range(args.steps)) / args.steps
+    total_ms = ev[0].elapsed_time(ev[2 * args.steps])
+    upd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)) / args.steps
+    ag_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps)) / args.steps
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    elems = torch.tensor([float(owned_elems)], device=device, dtype=torch.float64)
     if world > 1:
         t = torch.tensor([total_ms, upd_ms, ag_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, upd_ms, ag_ms = t.tolist()
+        dist.all_reduce(elems, op=dist.ReduceOp.SUM)
+    total_elems = int(elems.item())
     ms_per_step = total_ms / args.steps
-    value = n * world / (ms_per_step * 1e-3)
+    value = total_elems / (ms_per_step * 1e-3)
 
     # the kernel's own duration: steps are enqueued back to back, so the update interval between
-    # consecutive events is the kernel (plus a 48-byte hyper-parameter copy)
+    # consecutive events is the kernel (plus a 48-byte hyper-parameter copy); per rank, slowest rank
     peak, which = measured_peak()
-    achieved = BYTES_PER_ELEM * n / (upd_ms * 1e-3) / 1e9
+    per_rank = total_elems / world
+    achieved = bytes_per_elem * per_rank / (upd_ms * 1e-3) / 1e9
+    traffic = NCU_DRAM_BYTES_PER_ELEM * per_rank if (wl == "c2" and NCU_DRAM_BYTES_PER_ELEM) else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": which,
-                "traffic": None if NCU_DRAM_BYTES_PER_ELEM is None else NCU_DRAM_BYTES_PER_ELEM * n,
-                "algorithmic_bytes": BYTES_PER_ELEM * n, "kernel_ms": upd_ms,
+                "frac": achieved / peak, "peak_source": which, "traffic": traffic,
+                "algorithmic_bytes": bytes_per_elem * per_rank, "kernel_ms": upd_ms,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 
     # ---------------------------------------------------------------- end to end from host memory
     e2e = None
-    if not args.no_e2e:
-        del opt, st
-        shard.grad = None
-        del grad, shard, params, rpg
+    if not args.no_e2e and wl == "c2":
+        n = args.elems
+        for opt in steppers:
+            for p in opt.state:
+                p.grad = None
+        steppers.clear(); rpgs.clear()
+        del opt
         torch.cuda.empty_cache()
         n_host = n
         budget = host_mem_available_bytes() // max(world, 1)
@@ -336,21 +396,25 @@ def main():
                "ring_depth": hopt.offload_ring_depth}
 
     base = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and wl == "c2":
         base = cpu_baseline()
 
     if rank == 0:
+        label = WORKLOADS[wl]
+        if world > 1:
+            label += "; ZeRO-1 all-gather of the updated parameters inside the step"
+        l2 = ("rotating over 12 buffer sets of 128 MiB (1.5 GiB > L2)" if wl == "c1" else
+              "per-GPU inputs far exceed L2; no flush needed")
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "config 2: 2^30-element bf16 parameter shard per GPU, fp32 moments, "
-                                       "bf16 grads ~N(0,1e-3), t=100" +
-                                       (", ZeRO-1 all-gather of updated parameters inside the step" if world > 1 else ""),
-                           "elements_per_gpu": n, "l2": "inputs (12 GiB per GPU) far exceed L2; no flush needed",
+                "scaling": "weak" if wl in ("c2", "bf16", "c1") else "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": label, "elements_per_step": total_elems, "l2": l2,
+                           "math": "fast (approx sqrt/rcp in p')" if args.fast_math else "exact (IEEE sqrt/div)",
                            "parallelism": f"zero1x{world}" if world > 1 else "single"},
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
-                "update_only_value": n * world / (upd_ms * 1e-3)}
+                "update_only_value": total_elems / (upd_ms * 1e-3), "host_ms_per_step": host_ms}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

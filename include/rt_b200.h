@@ -19,7 +19,8 @@
  *     v' = fma(one_minus_beta2 * g, g, v * beta2)                adamw.py:191
  *     den = sqrt(v') / bias_correction2_sqrt + eps               adamw.py:193-195
  *     p' = (apply_decay ? p * decay : p) + (neg_step_size * m') / den   adamw.py:197-200
- *   every operation rounded to nearest-even fp32 separately except the two fma's.
+ *   every operation rounded to nearest-even fp32 separately except the two fma's
+ *   (rt_hyper.flags & RT_HYPER_FAST_MATH relaxes den and the quotient, see below).
  *   Write-back (adamw.py:204-222): a bf16 destination is stochastically rounded,
  *     out16 = ((bits(x) + r16) & 0xFFFF0000) >> 16                adamw.py:6-30
  *   an fp32 destination is copied, an fp16 destination is rounded to nearest-even.
@@ -76,8 +77,19 @@ typedef struct rt_hyper {
   float centralization;         /* f32(c); 0 disables (adamw.py:179-184) */
   uint32_t apply_decay;         /* weight_decay != 0 (adamw.py:197) */
   uint32_t step;                /* t; also the Philox counter word 2 */
-  uint32_t reserved;
+  uint32_t flags;               /* RT_HYPER_* bits; every row of one call must agree */
+  float inv_bias_correction2_sqrt; /* f32(1 / bias_correction2_sqrt); used by RT_HYPER_FAST_MATH */
+  uint32_t reserved[3];
 } rt_hyper;
+
+/* rt_hyper.flags */
+/* Approximate denominator and quotient: den = fma(sqrt.approx(v'), inv_bias_correction2_sqrt, eps),
+ * p' = pw + (neg_step_size * m') * rcp.approx(den).  m' and v' are unchanged (bit-exact); p' stays
+ * within 1e-6 relative of the exact contract (measured worst case in tests) but is no longer
+ * bit-identical to the CPU checker.  Off by default.  Cuts ~25 instructions per element, which
+ * matters for the all-bf16 variant (three Philox calls per eight elements) that is otherwise
+ * bound by instruction issue rather than HBM. */
+#define RT_HYPER_FAST_MATH 1u
 
 /* Fill an rt_hyper from the constructor-level values, in double precision, as
  * adamw.py:173-188 does.  Pure host arithmetic. */

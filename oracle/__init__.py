@@ -41,7 +41,9 @@ class Hyper(ctypes.Structure):
         ("centralization", ctypes.c_float),
         ("apply_decay", ctypes.c_uint32),
         ("step", ctypes.c_uint32),
-        ("reserved", ctypes.c_uint32),
+        ("flags", ctypes.c_uint32),
+        ("inv_bias_correction2_sqrt", ctypes.c_float),
+        ("reserved", ctypes.c_uint32 * 3),
     ]
 
 
@@ -94,6 +96,7 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0) -> Hyper:
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
+    h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 
 

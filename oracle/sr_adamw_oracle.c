@@ -174,6 +174,7 @@ void rto_hyper_fill(rt_hyper* out, double lr, double beta1, double beta2, double
   out->centralization = (float)centralization;
   out->apply_decay = weight_decay != 0.0;
   out->step = step;
+  out->inv_bias_correction2_sqrt = (float)(1.0 / (double)out->bias_correction2_sqrt);
 }
 
 int rto_num_threads(void) {

@@ -26,7 +26,11 @@ class Hyper(ctypes.Structure):
                 ("bias_correction2_sqrt", ctypes.c_float), ("eps", ctypes.c_float),
                 ("decay", ctypes.c_float), ("neg_step_size", ctypes.c_float),
                 ("centralization", ctypes.c_float), ("apply_decay", c_uint32),
-                ("step", c_uint32), ("reserved", c_uint32)]
+                ("step", c_uint32), ("flags", c_uint32),
+                ("inv_bias_correction2_sqrt", ctypes.c_float), ("reserved", c_uint32 * 3)]
+
+
+HYPER_FAST_MATH = 1
 
 
 class Debug(ctypes.Structure):
@@ -103,7 +107,7 @@ def check(rc: int, what: str = "librt_b200") -> None:
         raise kind(f"{what} failed ({rc}): {msg}")
 
 
-def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0) -> Hyper:
+def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math=False) -> Hyper:
     """The per-step scalars of ``adamw.py:173-188``: Python-double arithmetic written the way the
     reference writes it, then one rounding to fp32 each (what ATen does when a Python scalar
     meets an fp32 tensor)."""
@@ -121,6 +125,8 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0) -> Hyper:
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
+    h.flags = HYPER_FAST_MATH if fast_math else 0
+    h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 
 

@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported():
 
 
 def test_struct_sizes_match_header():
-    assert ctypes.sizeof(N.Hyper) == 48
+    assert ctypes.sizeof(N.Hyper) == 64
     assert ctypes.sizeof(N.TensorDesc) == 64
     assert ctypes.sizeof(N.Debug) == 48
     assert ctypes.sizeof(N.OffloadCfg) == 32

@@ -254,3 +254,47 @@ def test_large_flat_tensor_spot_checked_against_checker():
         assert bits_equal(ps, to_numpy(p[lo:hi])) == 0
         assert bits_equal(ms, to_numpy(m[lo:hi])) == 0
         assert bits_equal(vs, to_numpy(v[lo:hi])) == 0
+
+
+@pytest.mark.parametrize("kinds", [("bf16", "bf16", "bf16"), ("bf16", "bf16", "f32"), ("f32", "f32", "f32")])
+@pytest.mark.parametrize("step", [1, 11, 100])
+def test_fast_math_stays_within_the_fp32_tolerance(kinds, step):
+    """RT_HYPER_FAST_MATH: moments bit-exact, p' within 1e-6 relative (cancellation-safe
+    denominator) of the exact contract, bf16 parameters in {floor, ceil} of the kernel's own fp32."""
+    from ramtorch_b200 import _native as N
+    n = 200003
+    kp, kg, ks = kinds
+    p, g, m, v = synth(n, kp, kg, ks, 4, warm=step > 1)
+    dev = torch.device("cuda")
+    hn = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, step, fast_math=True)
+    ho = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, step)
+    tp, tg, tm, tv = (to_torch(a, k, dev) for a, k in zip((p, g, m, v), (kp, kg, ks, ks)))
+    taps = tuple(torch.empty(n, dtype=torch.float32, device=dev) for _ in range(3))
+    rng = np.random.default_rng(5)
+    rand_np = tuple(rng.integers(0, 65536, n, dtype=np.uint16) for _ in range(3))
+    rand_t = tuple(torch.from_numpy(r.view(np.int16).copy()).to(dev) for r in rand_np)
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, rand=rand_t, taps=taps)
+    # production (vectorised) kernel with the same flag, Philox draws
+    tp2, tg2, tm2, tv2 = (to_torch(a, k, dev) for a, k in zip((p, g, m, v), (kp, kg, ks, ks)))
+    F.adamw_sr_flat_(tp2, tg2, tm2, tv2, hn, seed=8, tensor_id=3)
+    torch.cuda.synchronize()
+    p_old = (oracle.bf16_bits_to_f32(p) if kp == "bf16" else p).astype(np.float64)
+    po, mo, vo = p.copy(), m.copy(), v.copy()
+    fp, fm, fv = oracle.adamw_sr(po, g, mo, vo, CODE[kp], CODE[kg], CODE[ks], ho, seed=8, tensor_id=3, want_f32=True)
+    assert bits_equal(taps[1].cpu().numpy(), fm) == 0
+    assert bits_equal(taps[2].cpu().numpy(), fv) == 0
+    got = taps[0].cpu().numpy().astype(np.float64)
+    den = np.maximum(np.abs(p_old), np.abs(fp.astype(np.float64) - p_old))
+    rel = np.abs(got - fp) / np.where(den > 0, den, 1)
+    assert rel.max() <= 1e-6, rel.max()
+    if kp == "bf16":
+        assert (oracle.sr_round_np(taps[0].cpu().numpy(), rand_np[0]) == to_numpy(tp)).all()
+    # production kernel: moments identical to the checker, parameters at most one step away and
+    # almost always identical
+    assert bits_equal(to_numpy(tm2), mo) == 0 and bits_equal(to_numpy(tv2), vo) == 0
+    if kp == "bf16":
+        d = np.abs(to_numpy(tp2).astype(np.int64) - po.astype(np.int64))
+        assert d.max() <= 1 and (d != 0).mean() < 1e-3
+    else:
+        rel2 = np.abs(to_numpy(tp2).astype(np.float64) - po) / np.where(den > 0, den, 1)
+        assert rel2.max() <= 1e-6
