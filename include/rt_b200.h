@@ -170,6 +170,26 @@ int rt_adamw_sr_multi(rt_plan* plan, const rt_hyper* hyper, int hyper_count,
                       uint64_t seed, void* cuda_stream);
 
 /*
+ * ZeRO-1 fused redistribution (replaces the per-tensor dist.broadcast of zero1.py:78-91 for
+ * the tensors this rank owns).  `local_base`/`bytes` describe a parameter region of this GPU
+ * that every peer maps at the same layout; peer_base[k] is the same region in peer k's
+ * memory as mapped into this process (CUDA IPC / VMM peer mapping).  While set, every
+ * rt_adamw_sr_multi of the plan also stores each updated parameter that lies inside the
+ * region into all peers' copies with plain peer stores, so the owners' values reach every
+ * rank without a separate all-gather pass.  The caller still has to order the peers' reads
+ * after all ranks' launches (any barrier-like collective on the same streams).
+ * push == NULL or n_peers == 0 clears it.
+ */
+#define RT_MAX_PEERS 15
+typedef struct rt_push {
+  void* local_base;
+  int64_t bytes;
+  int n_peers;
+  void* peer_base[RT_MAX_PEERS];
+} rt_push;
+int rt_plan_set_push(rt_plan* plan, const rt_push* push);
+
+/*
  * Multi-tensor step for callers that must not allocate.  No counterpart in the reference.
  *
  * rt_plan_create keeps its tensor, chunk and hyper-parameter tables in memory it obtains from

@@ -50,6 +50,14 @@ class OffloadCfg(ctypes.Structure):
                 ("staging_bytes", c_int64)]
 
 
+MAX_PEERS = 15
+
+
+class Push(ctypes.Structure):
+    _fields_ = [("local_base", c_void_p), ("bytes", c_int64), ("n_peers", c_int),
+                ("peer_base", c_void_p * MAX_PEERS)]
+
+
 class Stats(ctypes.Structure):
     _fields_ = [("kernel_launches", c_uint64), ("h2d_bytes", c_uint64), ("d2h_bytes", c_uint64),
                 ("h2d_copies", c_uint64), ("d2h_copies", c_uint64)]
@@ -69,6 +77,7 @@ _SIGNATURES = {
     "rt_plan_set_grads": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_void_p]),
     "rt_plan_launches": (c_int, [c_void_p]),
     "rt_adamw_sr_multi": (c_int, [c_void_p, ctypes.POINTER(Hyper), c_int, c_uint64, c_void_p]),
+    "rt_plan_set_push": (c_int, [c_void_p, ctypes.POINTER(Push)]),
     "rt_adamw_sr_multi_static": (c_int, [ctypes.POINTER(TensorDesc), c_int64, ctypes.POINTER(Hyper), c_int,
                                          c_uint64, c_void_p]),
     "rt_offload_staging_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),

@@ -17,6 +17,8 @@ reference's shape.
 from __future__ import annotations
 
 import hashlib
+import os
+import warnings
 from typing import Dict, List, Optional
 
 import torch
@@ -39,6 +41,14 @@ class Bucket:
         self.grad_views: List[Optional[torch.Tensor]] = []
         self.ready = 0                       # gradients accumulated since the last reduction
         self.expected = 0                    # parameters that take part in backward
+        # fused redistribution: `flat` is peer-mapped and the optimizer kernel stores updated
+        # parameters straight into every peer's copy
+        self.peer_ptrs: Optional[List[int]] = None   # base address of every rank's flat buffer
+        self.rank = -1                       # this process's rank among the peers
+        self.symm = None                     # keeps the peer mapping alive
+        self.pushed = False                  # set by the optimizer after a pushing launch
+        self.mode = None                     # None (undecided) | "push" | "gather"
+        self.checks = 0
 
     def rank_segment(self, buf: torch.Tensor, rank: int) -> torch.Tensor:
         return buf[rank * self.segment:(rank + 1) * self.segment]
@@ -125,13 +135,38 @@ class ShardPlan:
         self.verified = True
 
     # ------------------------------------------------------------------ flattening
+    def _allocate_flat(self, b: Bucket) -> torch.Tensor:
+        """The flat parameter buffer of a bucket.  On NCCL ranks with CUDA parameters it is
+        allocated as peer-mapped ("symmetric") memory so that the optimizer kernel can store the
+        owners' new values directly into every rank's copy; anything else gets plain memory and
+        the all-gather path.  Set RT_ZERO_FUSED_PUSH=0 to force the all-gather path."""
+        n = b.segment * self.world_size
+        want = (b.device.type == "cuda" and self.world_size > 1 and self.world_size - 1 <= 15 and
+                dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl" and
+                dist.get_world_size() == self.world_size and os.environ.get("RT_ZERO_FUSED_PUSH", "1") != "0")
+        if want:
+            try:
+                import torch.distributed._symmetric_memory as symm
+                flat = symm.empty(n, dtype=b.dtype, device=b.device)
+                handle = symm.rendezvous(flat, dist.group.WORLD)
+                b.peer_ptrs = [int(q) for q in handle.buffer_ptrs]
+                b.rank = int(handle.rank)
+                b.symm = handle
+                flat.zero_()
+                _PUSH_BUCKETS.setdefault(b.device.index, []).append(b)
+                return flat
+            except Exception as e:  # pragma: no cover - depends on driver / topology
+                warnings.warn(f"peer-mapped parameter buffer unavailable ({e!r}); using NCCL all-gather")
+                b.peer_ptrs = None
+        return torch.zeros(n, dtype=b.dtype, device=b.device)
+
     def flatten_params(self) -> None:
         """Move every bucket's parameters into its flat buffer and re-point ``p.data`` at the views."""
         if self.flattened:
             return
         with torch.no_grad():
             for b in self.buckets.values():
-                b.flat = torch.zeros(b.segment * self.world_size, dtype=b.dtype, device=b.device)
+                b.flat = self._allocate_flat(b)
                 for p, off in zip(b.params, b.offset):
                     view = b.flat[off:off + p.numel()].view(p.shape)
                     view.copy_(p.data)
@@ -158,6 +193,23 @@ class ShardPlan:
 
 
 _PLANS: Dict[int, tuple] = {}
+_PUSH_BUCKETS: Dict[int, List[Bucket]] = {}   # cuda device index -> buckets with peer-mapped buffers
+
+
+def all_push_buckets() -> List[Bucket]:
+    return [b for bs in _PUSH_BUCKETS.values() for b in bs]
+
+
+def push_bucket_for(device_index: int, data_ptrs) -> Optional[Bucket]:
+    """The peer-mapped bucket on ``device_index`` that holds most of the given parameter addresses."""
+    best, best_hits = None, 0
+    for b in _PUSH_BUCKETS.get(device_index, []):
+        lo = b.flat.data_ptr()
+        hi = lo + b.flat.numel() * b.flat.element_size()
+        hits = sum(1 for q in data_ptrs if lo <= q < hi)
+        if hits > best_hits:
+            best, best_hits = b, hits
+    return best
 
 
 def plan_for(rank_param_groups) -> ShardPlan:

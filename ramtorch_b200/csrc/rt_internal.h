@@ -26,6 +26,14 @@ struct DevTensor {
 };
 constexpr uint32_t kVecOk = 1u;  // all four pointers are 16-byte aligned
 
+// Peer copies of a shared parameter region (kernel argument; n == 0 disables).
+struct PushTable {
+  const char* local;          // base of the region in this GPU's memory
+  int64_t bytes;
+  int n;                      // number of peers
+  char* base[RT_MAX_PEERS];   // the region's base in each peer's memory, as mapped here
+};
+
 constexpr int kThreads = 256;
 constexpr int kChunkElems = kThreads * 8 * 4;  // elements one CTA walks through
 
@@ -50,7 +58,8 @@ inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 // nblocks chunks, or they are null and `one`/`one_h` describe a single tensor.
 int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* chunks,
                  const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
-                 uint64_t seed, int64_t nblocks, cudaStream_t stream, bool fast);
+                 uint64_t seed, int64_t nblocks, cudaStream_t stream, bool fast,
+                 const PushTable* push);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
 int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,

@@ -67,6 +67,20 @@ class _DevicePlan:
                 "rt_plan_create")
         self.launches = N.lib().rt_plan_launches(self.handle)
         self.grad_ptrs = (N.c_void_p * len(descs))()
+        # ZeRO-1: when the parameters live in a peer-mapped flat buffer, let the kernel store the
+        # updated values into every peer's copy as well
+        from .._shard_plan import push_bucket_for
+        self.push_bucket = push_bucket_for(device_index, [d.p for d in descs])
+        if self.push_bucket is not None:
+            b = self.push_bucket
+            peers = [q for r, q in enumerate(b.peer_ptrs) if r != b.rank]
+            push = N.Push()
+            push.local_base = b.flat.data_ptr()
+            push.bytes = b.flat.numel() * b.flat.element_size()
+            push.n_peers = len(peers)
+            for k, q in enumerate(peers):
+                push.peer_base[k] = q
+            N.check(N.lib().rt_plan_set_push(self.handle, ctypes.byref(push)), "rt_plan_set_push")
 
     def close(self):
         if self.handle:
@@ -132,6 +146,7 @@ class AdamW(Optimizer):
         self._staging = {}    # cuda device index -> uint8 tensor
         self._keepalive = []
         self._warned_pageable = False
+        self._push_marks = []  # peer-mapped buckets the last validated step fully redistributed
         self._fast = None     # cache that lets an unchanged, fully resident step skip re-validation
         self.last_step_info = {}
 
@@ -304,6 +319,7 @@ class AdamW(Optimizer):
                         "rt_adamw_sr_offload")
             launches += (pd.numel() + chunk - 1) // chunk
 
+        self._mark_pushed(resident, streamed)
         self.last_step_info = dict(launches=launches, resident=sum(map(len, resident.values())),
                                    streamed=len(streamed))
         if len(resident) == 1 and not streamed and not self._keepalive:
@@ -314,6 +330,30 @@ class AdamW(Optimizer):
                 torch.cuda.current_stream(index).synchronize()
             self._keepalive.clear()
         return loss
+
+    def _mark_pushed(self, resident, streamed):
+        """ZeRO-1 fused redistribution bookkeeping: a peer-mapped parameter bucket counts as
+        redistributed by this step unless this step changed a parameter inside it WITHOUT the
+        kernel's peer stores (a streamed tensor, or a tensor outside the plan's shared region)."""
+        from .._shard_plan import all_push_buckets
+        self._push_marks = []
+        buckets = all_push_buckets()
+        if not buckets:
+            return
+        plain = [e[1].data_ptr() for e in streamed]          # (index, pd, ...) -> pd
+        for index, entries in resident.items():
+            pushing = self._plans[index].push_bucket
+            for pd, *_ in entries:
+                q = pd.data_ptr()
+                if pushing is None or not (pushing.flat.data_ptr() <= q <
+                                           pushing.flat.data_ptr() + pushing.flat.numel() * pushing.flat.element_size()):
+                    plain.append(q)
+        for b in buckets:
+            lo = b.flat.data_ptr()
+            hi = lo + b.flat.numel() * b.flat.element_size()
+            if not any(lo <= q < hi for q in plain):
+                b.pushed = True
+                self._push_marks.append(b)
 
     # ------------------------------------------------------------------ repeat-step fast path
     def _remember_fast(self, index, hyper_index):
@@ -379,6 +419,8 @@ class AdamW(Optimizer):
                     "rt_plan_set_grads")
             N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(rows), self.seed & (2 ** 64 - 1), stream),
                     "rt_adamw_sr_multi")
+        for bucket in self._push_marks:
+            bucket.pushed = True
         self.last_step_info = dict(launches=plan.launches, resident=len(params), streamed=0, fast=True)
         if self.sync:
             torch.cuda.current_stream(index).synchronize()

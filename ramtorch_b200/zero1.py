@@ -73,11 +73,61 @@ def broadcast_zero_params(rank_param_groups, async_op=True):
     rank = dist.get_rank()
     works = []
     with torch.no_grad():
+        barrier_needed = False
         for bucket in plan.buckets.values():
-            mine = bucket.rank_segment(bucket.flat, rank)
-            works.append(dist.all_gather_into_tensor(bucket.flat, mine, async_op=async_op))
+            if _owners_pushed(plan, bucket, rank):
+                barrier_needed = True          # values already sit in every rank's buffer
+            else:
+                mine = bucket.rank_segment(bucket.flat, rank)
+                works.append(dist.all_gather_into_tensor(bucket.flat, mine, async_op=async_op))
+            bucket.pushed = False
         for param, owner in plan.loose:
             works.append(dist.broadcast(param.data, src=owner, async_op=async_op))
+        if barrier_needed and not works:
+            # nothing else orders this rank's reads after the other ranks' kernels: a one-element
+            # all-reduce on the same stream does (it completes only after every rank's launch has)
+            works.append(dist.all_reduce(_token(plan), async_op=async_op))
         for work in works:
             if work is not None:
                 work.wait()
+
+
+_CHECKED_CALLS = 3
+
+
+def _token(plan: ShardPlan) -> torch.Tensor:
+    tok = getattr(plan, "_token", None)
+    if tok is None:
+        device = next(b.device for b in plan.buckets.values() if b.peer_ptrs is not None)
+        tok = plan._token = torch.zeros(1, dtype=torch.int32, device=device)
+    return tok
+
+
+def _owners_pushed(plan: ShardPlan, bucket, rank: int) -> bool:
+    """Whether this bucket's owners already stored their updated parameters into every rank's
+    buffer (the fused path of ``AdamW.step``), so the all-gather can be skipped.
+
+    All ranks must take the same branch.  During the first few calls the ranks agree through a
+    tiny all-reduce (a rank that owns nothing in the bucket, or whose optimizer pushed, votes yes);
+    after that the agreed mode is kept.  The very first call always gathers, which also makes
+    ranks that started from different initial values consistent."""
+    if bucket.peer_ptrs is None:
+        return False
+    if bucket.mode == "gather":
+        return False
+    owns = any(o == rank for o in bucket.owner)
+    vote = bucket.pushed or not owns
+    if bucket.mode == "push":
+        if not vote:
+            raise RuntimeError("ZeRO-1 fused redistribution was agreed on, but this rank's optimizer did not "
+                               "store its updated parameters into the peers' buffers this step; use "
+                               "ramtorch_b200.AdamW for every rank or set RT_ZERO_FUSED_PUSH=0")
+        return True
+    first = bucket.checks == 0
+    bucket.checks += 1
+    flag = torch.tensor([1 if vote else 0], dtype=torch.int32, device=bucket.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    agreed = bool(flag.item())
+    if bucket.checks >= _CHECKED_CALLS:
+        bucket.mode = "push" if agreed else "gather"
+    return agreed and not first

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 SHAPES = [(257, 64), (64,), (1000, 33), (33,), (4096,), (8, 8, 8), (70001,), (5,), (129, 128)]
 HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
-STEPS = 3
+STEPS = 5
 
 
 def _params(device):
@@ -34,8 +34,9 @@ def _groups(params):
             {"params": [p for p in params if p.dim() > 1]}]
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, fused):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["RT_ZERO_FUSED_PUSH"] = "1" if fused else "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -56,6 +57,9 @@ def _worker(rank, world, port, out):
             for p in params:
                 p.grad = None if step % 2 == 0 else p.grad.zero_()
         torch.cuda.synchronize()
+        from ramtorch_b200._shard_plan import plan_for
+        modes = sorted({str(b.mode) for b in plan_for(rpg).buckets.values()})
+        assert modes == (["push"] if fused else ["None"]), modes
         out.put((rank, "ok", [p.detach().float().cpu() for p in params]))
     except Exception as e:
         import traceback
@@ -77,8 +81,9 @@ def _single_process(world):
     return [p.detach().float().cpu() for p in params]
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["peer-push", "all-gather"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_zero_loop_matches_single_process(world):
+def test_zero_loop_matches_single_process(world, fused):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
@@ -86,7 +91,7 @@ def test_zero_loop_matches_single_process(world):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out, fused)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted((out.get() for _ in procs), key=lambda r: r[0])
