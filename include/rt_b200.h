@@ -132,7 +132,18 @@ int rt_sr_round_bf16(void* target_bf16, const float* source_f32, int64_t n,
 int rt_adamw_sr_flat(void* p, const void* g, void* m, void* v, int64_t n,
                      int p_dtype, int g_dtype, int state_dtype,
                      const rt_hyper* hyper, uint64_t seed, uint32_t tensor_id,
-                     int64_t index0, const rt_debug* debug, void* cuda_stream);
+                     int64_t index0, const float* row_mean, int64_t row_len,
+                     const rt_debug* debug, void* cuda_stream);
+
+/*
+ * a8 -- gradient centralization (adamw.py:179-184): out[r] = mean over row r of g, fp32, for a
+ * gradient viewed as rows x row_len (rows = size of dim 0, or 1 for tensors with fewer than two
+ * dimensions, which the reference reduces as a whole).  The fused kernels subtract
+ * centralization * out[(index0 + i) / row_len] from g[i] when a tensor carries row_mean and its
+ * hyper row has centralization != 0 (row_len == 0: the whole tensor is one row).
+ */
+int rt_row_means(const void* g, int g_dtype, int64_t rows, int64_t row_len, float* out,
+                 void* cuda_stream);
 
 /*
  * Multi-tensor plan: the tensor table of an optimizer (one row per parameter that has a
@@ -151,6 +162,7 @@ typedef struct rt_tensor_desc {
   uint32_t hyper_index; /* row of the hyper table passed at step time */
   uint8_t p_dtype, g_dtype, state_dtype, reserved0;
   uint32_t row_len;     /* elements per row for centralization; 0 = whole tensor is one row */
+  const float* row_mean; /* device array of row means (rt_row_means) or NULL */
 } rt_tensor_desc;
 
 typedef struct rt_plan rt_plan;

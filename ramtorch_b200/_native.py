@@ -42,7 +42,8 @@ class TensorDesc(ctypes.Structure):
     _fields_ = [("p", c_void_p), ("g", c_void_p), ("m", c_void_p), ("v", c_void_p),
                 ("numel", c_int64), ("index0", c_int64), ("tensor_id", c_uint32),
                 ("hyper_index", c_uint32), ("p_dtype", ctypes.c_uint8), ("g_dtype", ctypes.c_uint8),
-                ("state_dtype", ctypes.c_uint8), ("reserved0", ctypes.c_uint8), ("row_len", c_uint32)]
+                ("state_dtype", ctypes.c_uint8), ("reserved0", ctypes.c_uint8), ("row_len", c_uint32),
+                ("row_mean", c_void_p)]
 
 
 class OffloadCfg(ctypes.Structure):
@@ -70,8 +71,9 @@ _SIGNATURES = {
     "rt_sr_round_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_uint64, c_uint32, c_uint32,
                                  c_uint32, c_void_p]),
     "rt_adamw_sr_flat": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
-                                 ctypes.POINTER(Hyper), c_uint64, c_uint32, c_int64,
+                                 ctypes.POINTER(Hyper), c_uint64, c_uint32, c_int64, c_void_p, c_int64,
                                  ctypes.POINTER(Debug), c_void_p]),
+    "rt_row_means": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "rt_plan_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(TensorDesc), c_int64, c_int]),
     "rt_plan_destroy": (c_int, [c_void_p]),
     "rt_plan_set_grads": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_void_p]),

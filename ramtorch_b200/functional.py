@@ -50,7 +50,20 @@ def sr_round_bf16_(target: torch.Tensor, source: torch.Tensor, *, rand16: torch.
     return target
 
 
-def adamw_sr_flat_(p, g, m, v, hyper: N.Hyper, *, seed=0, tensor_id=0, index0=0,
+def row_means(g: torch.Tensor, rows: int, row_len: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 mean of each of the ``rows`` rows of ``row_len`` elements of ``g`` (``rt_row_means``)."""
+    _need_cuda(g, "g")
+    if rows * row_len != g.numel():
+        raise ValueError("rows * row_len must equal g.numel()")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=g.device)
+    with torch.cuda.device(g.device):
+        N.check(N.lib().rt_row_means(g.data_ptr(), _code(g, "g"), rows, row_len, out.data_ptr(),
+                                     N.stream_ptr(g.device)), "rt_row_means")
+    return out
+
+
+def adamw_sr_flat_(p, g, m, v, hyper: N.Hyper, *, seed=0, tensor_id=0, index0=0, row_mean=None, row_len=0,
                    rand=(None, None, None), taps=(None, None, None)) -> None:
     """One fused step over one device-resident tensor, in place (``rt_adamw_sr_flat``).
 
@@ -82,5 +95,6 @@ def adamw_sr_flat_(p, g, m, v, hyper: N.Hyper, *, seed=0, tensor_id=0, index0=0,
         N.check(N.lib().rt_adamw_sr_flat(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n,
                                          _code(p, "p"), _code(g, "g"), _code(m, "m"),
                                          ctypes.byref(hyper), seed & (2**64 - 1), tensor_id, index0,
+                                         None if row_mean is None else row_mean.data_ptr(), row_len,
                                          ctypes.byref(dbg) if dbg is not None else None,
                                          N.stream_ptr(p.device)), "rt_adamw_sr_flat")

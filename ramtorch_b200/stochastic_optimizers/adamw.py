@@ -144,6 +144,7 @@ class AdamW(Optimizer):
         self.fast_math = bool(fast_math)
         self._plans = {}      # cuda device index -> _DevicePlan
         self._staging = {}    # cuda device index -> uint8 tensor
+        self._row_scratch = {}  # cuda device index -> fp32 row means for centralization
         self._keepalive = []
         self._warned_pageable = False
         self._push_marks = []  # peer-mapped buckets the last validated step fully redistributed
@@ -219,6 +220,7 @@ class AdamW(Optimizer):
         resident = {}   # device index -> list of (p, grad, ema, ema_sq, tensor_id, hyper_index)
         streamed = []   # (device index, p, grad, ema, ema_sq, tensor_id, hyper_index)
         hyper_rows, hyper_index = [], {}
+        centered = {}   # device index -> {position in resident[index]: number of rows}
         late = []
         for gi, group in enumerate(self.param_groups):
             for p in group["params"]:
@@ -232,8 +234,6 @@ class AdamW(Optimizer):
         self._allocate_states(late)  # lazy state for parameters added late (adamw.py:125-148)
 
         for gi, group in enumerate(self.param_groups):
-            if group["centralization"] != 0:
-                raise NotImplementedError("centralization != 0 is not available in this build yet")
             for p in group["params"]:
                 grad = p.grad
                 if grad is None:
@@ -272,7 +272,15 @@ class AdamW(Optimizer):
                 entry = (pd, grad, ema, ema_sq, self._tensor_ids[p], hi)
                 if pd.is_cuda and grad.is_cuda and ema.is_cuda and ema_sq.is_cuda:
                     resident.setdefault(index, []).append(entry)
+                    if group["centralization"] != 0:
+                        # rows = size of dim 0; tensors with fewer than two dimensions are one row
+                        # (the reference's mean over an empty dim tuple reduces everything)
+                        rows = pd.shape[0] if pd.dim() >= 2 else 1
+                        centered.setdefault(index, {})[len(resident[index]) - 1] = rows
                 else:
+                    if group["centralization"] != 0:
+                        raise NotImplementedError("centralization != 0 needs parameter, gradient and moments "
+                                                  "on the GPU (it is not available on the streamed path)")
                     streamed.append((index,) + entry)
 
         if len(hyper_rows) > 1024:
@@ -285,10 +293,11 @@ class AdamW(Optimizer):
         for index, entries in resident.items():
             used.add(index)
             with torch.cuda.device(index):
-                plan = self._plan_for(index, entries)
+                stream = N.stream_ptr(index)
+                row_info = self._row_means(lib, index, entries, centered.get(index, {}), stream)
+                plan = self._plan_for(index, entries, row_info)
                 for k, e in enumerate(entries):
                     plan.grad_ptrs[k] = e[1].data_ptr()
-                stream = N.stream_ptr(index)
                 N.check(lib.rt_plan_set_grads(plan.handle, plan.grad_ptrs, stream), "rt_plan_set_grads")
                 N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(hyper_rows), seed, stream),
                         "rt_adamw_sr_multi")
@@ -322,7 +331,7 @@ class AdamW(Optimizer):
         self._mark_pushed(resident, streamed)
         self.last_step_info = dict(launches=launches, resident=sum(map(len, resident.values())),
                                    streamed=len(streamed))
-        if len(resident) == 1 and not streamed and not self._keepalive:
+        if len(resident) == 1 and not streamed and not self._keepalive and not centered:
             self._remember_fast(next(iter(resident)), hyper_index)
         if self.sync:
             # results are visible to the host when step() returns (adamw.py:232)
@@ -426,9 +435,33 @@ class AdamW(Optimizer):
             torch.cuda.current_stream(index).synchronize()
         return True
 
-    def _plan_for(self, index, entries) -> _DevicePlan:
+    def _row_means(self, lib, index, entries, rows_of, stream):
+        """Gradient centralization (adamw.py:179-184): fill a per-device scratch buffer with the
+        row means of every centralized gradient; returns {entry position: (address, row_len)}."""
+        if not rows_of:
+            return {}
+        total = sum(rows_of.values())
+        scratch = self._row_scratch.get(index)
+        if scratch is None or scratch.numel() < total:
+            scratch = torch.empty(total, dtype=torch.float32, device=torch.device("cuda", index))
+            self._row_scratch[index] = scratch
+        info, off = {}, 0
+        for k, rows in rows_of.items():
+            grad = entries[k][1]
+            row_len = grad.numel() // rows if rows else 0
+            if rows and row_len:
+                addr = scratch.data_ptr() + 4 * off
+                N.check(lib.rt_row_means(grad.data_ptr(), N.DTYPE_CODE[grad.dtype], rows, row_len, addr, stream),
+                        "rt_row_means")
+                info[k] = (addr, row_len if rows > 1 else 0)
+            off += rows
+        return info
+
+    def _plan_for(self, index, entries, row_info=None) -> _DevicePlan:
+        row_info = row_info or {}
         signature = [(pd.data_ptr(), ema.data_ptr(), ema_sq.data_ptr(), pd.numel(), pd.dtype,
-                      grad.dtype, ema.dtype, tid, hi) for pd, grad, ema, ema_sq, tid, hi in entries]
+                      grad.dtype, ema.dtype, tid, hi, row_info.get(k))
+                     for k, (pd, grad, ema, ema_sq, tid, hi) in enumerate(entries)]
         plan = self._plans.get(index)
         if plan is not None and plan.signature == signature:
             return plan
@@ -436,8 +469,10 @@ class AdamW(Optimizer):
             torch.cuda.current_stream(index).synchronize()
             plan.close()
         descs = []
-        for pd, grad, ema, ema_sq, tid, hi in entries:
+        for k, (pd, grad, ema, ema_sq, tid, hi) in enumerate(entries):
             d = N.TensorDesc()
+            if k in row_info:
+                d.row_mean, d.row_len = row_info[k]
             d.p, d.g, d.m, d.v = pd.data_ptr(), grad.data_ptr(), ema.data_ptr(), ema_sq.data_ptr()
             d.numel, d.index0, d.tensor_id, d.hyper_index = pd.numel(), 0, tid, hi
             d.p_dtype, d.g_dtype, d.state_dtype = (N.DTYPE_CODE[pd.dtype], N.DTYPE_CODE[grad.dtype],

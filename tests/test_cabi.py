@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported():
 
 def test_struct_sizes_match_header():
     assert ctypes.sizeof(N.Hyper) == 64
-    assert ctypes.sizeof(N.TensorDesc) == 64
+    assert ctypes.sizeof(N.TensorDesc) == 72
     assert ctypes.sizeof(N.Debug) == 48
     assert ctypes.sizeof(N.OffloadCfg) == 32
     assert ctypes.sizeof(N.Stats) == 40
@@ -50,13 +50,13 @@ def test_argument_errors_are_reported_before_any_launch():
     buf = (ctypes.c_uint8 * 64)()
     ptr = ctypes.addressof(buf)
     hp = ctypes.byref(h)
-    assert lib.rt_adamw_sr_flat(None, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 0, None, None) == -1
+    assert lib.rt_adamw_sr_flat(None, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 0, None, 0, None, None) == -1
     assert b"non-null" in lib.rt_last_error()
-    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 7, 0, hp, 0, 0, 0, None, None) == -2
-    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, -1, 0, 0, 0, hp, 0, 0, 0, None, None) == -3
-    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 4, None, None) == -3
-    assert lib.rt_adamw_sr_flat(ptr + 1, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 0, None, None) == -4
-    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 0, 0, None, 0, 0, 0, None, None) == -1
+    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 7, 0, hp, 0, 0, 0, None, 0, None, None) == -2
+    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, -1, 0, 0, 0, hp, 0, 0, 0, None, 0, None, None) == -3
+    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 4, None, 0, None, None) == -3
+    assert lib.rt_adamw_sr_flat(ptr + 1, ptr, ptr, ptr, 8, 0, 0, 0, hp, 0, 0, 0, None, 0, None, None) == -4
+    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 8, 0, 0, 0, None, 0, 0, 0, None, 0, None, None) == -1
     assert lib.rt_sr_round_bf16(None, ptr, 8, None, 0, 0, 0, 0, None) == -1
     assert lib.rt_plan_destroy(None) == -5
     assert lib.rt_offload_staging_bytes(12, 3, 0, 0, 0, 1, 1, 1, 1) == -6
@@ -70,5 +70,5 @@ def test_zero_length_calls_are_noops():
     h = N.make_hyper(1e-3, (0.9, 0.999), 1e-8, 0.0, 1)
     buf = (ctypes.c_uint8 * 64)()
     ptr = ctypes.addressof(buf)
-    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 0, 0, 0, 0, ctypes.byref(h), 0, 0, 0, None, None) == 0
+    assert lib.rt_adamw_sr_flat(ptr, ptr, ptr, ptr, 0, 0, 0, 0, ctypes.byref(h), 0, 0, 0, None, 0, None, None) == 0
     assert lib.rt_sr_round_bf16(ptr, ptr, 0, None, 0, 0, 0, 0, None) == 0

@@ -298,3 +298,35 @@ def test_fast_math_stays_within_the_fp32_tolerance(kinds, step):
     else:
         rel2 = np.abs(to_numpy(tp2).astype(np.float64) - po) / np.where(den > 0, den, 1)
         assert rel2.max() <= 1e-6
+
+
+@pytest.mark.parametrize("shape", [(37, 111), (1, 1000), (5000, 8), (100003,), (64, 4096)])
+@pytest.mark.parametrize("kind", ["bf16", "f32"])
+def test_row_means_kernel(shape, kind):
+    g = torch.randn(shape, generator=torch.Generator().manual_seed(7)) * 1e-3 + 2e-4
+    g = g.to(TORCH_DT[kind]).cuda()
+    rows = shape[0] if len(shape) >= 2 else 1
+    got = F.row_means(g.reshape(-1), rows, g.numel() // rows).cpu().numpy().astype(np.float64)
+    want = g.double().reshape(rows, -1).mean(dim=1).cpu().numpy()
+    scale = g.double().abs().reshape(rows, -1).mean(dim=1).cpu().numpy()
+    assert (np.abs(got - want) <= 2e-6 * scale + 1e-12).all()
+
+
+@pytest.mark.parametrize("shape", [(37, 111), (64, 4096), (100003,)])
+def test_centralized_step_is_bit_exact_given_the_same_row_means(shape):
+    from ramtorch_b200 import _native as N
+    n = int(np.prod(shape))
+    p, g, m, v = synth(n, "bf16", "bf16", "bf16", 12)
+    dev = torch.device("cuda")
+    tp, tg, tm, tv = (to_torch(a, "bf16", dev) for a in (p, g, m, v))
+    rows = shape[0] if len(shape) >= 2 else 1
+    row_len = n // rows
+    means = F.row_means(tg, rows, row_len)
+    hn = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, 5, centralization=0.5)
+    ho = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, 5, centralization=0.5)
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, seed=2, tensor_id=9, row_mean=means, row_len=row_len if rows > 1 else 0)
+    torch.cuda.synchronize()
+    oracle.adamw_sr(p, g, m, v, oracle.BF16, oracle.BF16, oracle.BF16, ho, seed=2, tensor_id=9,
+                    row_mean=means.cpu().numpy(), row_len=row_len if rows > 1 else 0)
+    for t, want in zip((tp, tm, tv), (p, m, v)):
+        assert bits_equal(to_numpy(t), want) == 0
