@@ -209,13 +209,119 @@ def ragged_shapes(count=20000, lo=64, hi=4194304, seed=0):
     return [(int(s),) if s < 16384 else (int(s) // 1024, 1024) for s in sizes]
 
 
+def link_ceiling(device, nbytes=1 << 30, reps=4):
+    """Pinned cudaMemcpyAsync rates of this box: each direction alone and both at once (GB/s)."""
+    import torch
+    h_in = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    h_out = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    d_out = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def run(h2d, d2h, n):
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        for _ in range(n):
+            if h2d:
+                with torch.cuda.stream(s_in):
+                    d_in.copy_(h_in, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s_out):
+                    h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.synchronize(device)
+        return nbytes * n / (time.perf_counter() - t0) / 1e9
+
+    run(True, True, 1)
+    return {"h2d_alone_gbs": run(True, False, reps), "d2h_alone_gbs": run(False, True, reps),
+            "both_each_gbs": run(True, True, reps)}
+
+
 WORKLOADS = {
     "c2": "config 2: one 2^30-element bf16 parameter shard per GPU, fp32 moments, bf16 grads ~N(0,1e-3), t=100",
     "bf16": "2^30-element bf16 parameter shard per GPU, bf16 moments (14 B/element), t=100",
     "c1": "config 1: 16,777,216-element bf16 parameter, bf16 moments, t=11, rotating over 12 buffer sets",
     "c3": "config 3: Llama-style 32-layer decoder shapes (291 tensors, 6.74e9 elements), bf16 moments, ZeRO-1",
     "c5": "config 5: 20,000 ragged bf16 tensors, sizes log-uniform in [64, 4194304], bf16 moments, ZeRO-1",
+    "c4": "config 4: 8e9 bf16 parameters + bf16 moments in pinned host RAM (60 tensors of 2^27 elements, split "
+          "over the ranks), gradients in pinned host RAM too (where the reference's Linear leaves them), streamed "
+          "in 256 MiB chunks per tensor through a 2-slot ring",
 }
+
+
+def run_c4(args, device, rank, world, warmup):
+    """Host-offloaded step: parameters and moments in pinned CPU RAM, streamed through the GPU."""
+    import torch
+    import torch.distributed as dist
+    from ramtorch_b200 import AdamW, _native as N
+    n_tensors, n_each = 60, 1 << 27
+    mine = [k for k in range(n_tensors) if k % world == rank]
+    budget = host_mem_available_bytes() // max(world, 1)
+    while len(mine) * n_each * 8 * 1.2 > budget and len(mine) > 1:
+        mine = mine[:-1]
+    params = [torch.empty(n_each, dtype=torch.bfloat16, pin_memory=True) for _ in mine]
+    opt = AdamW(params, dtype=torch.bfloat16, storage_device="cpu", seed=0, offload_chunk_elems=n_each,
+                offload_ring_depth=2, fast_math=args.fast_math, **HP)
+    scratch = torch.empty(n_each, dtype=torch.float32, device=device)
+    for p in params:
+        st = opt.state[p]
+        p.copy_(scratch.normal_(0, 0.02)); st["ema"].copy_(scratch.normal_(0, 1e-3))
+        st["ema_squared"].copy_(scratch.normal_(0, 1e-6).abs_())
+        st["step"] = START_STEP
+        p.grad = torch.empty(n_each, dtype=torch.bfloat16, pin_memory=True)
+        p.grad.copy_(scratch.normal_(0, 1e-3))
+    del scratch
+    ceiling = link_ceiling(device) if rank == 0 else None
+    steps = max(1, min(args.steps, 3))
+    opt.step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(device.index) if rank == 0 else None
+    s0 = N.stats()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        opt.step()
+        _ = float(params[0][0])
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    s1 = N.stats()
+    ms = e0.elapsed_time(e1) / steps
+    elems = torch.tensor([float(len(mine) * n_each)], device=device, dtype=torch.float64)
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+        dist.all_reduce(elems, op=dist.ReduceOp.SUM)
+    total = int(elems.item())
+    h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) / steps
+    d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) / steps
+    if rank == 0:
+        value = total / (ms * 1e-3)
+        link = {"h2d_gbs_per_gpu": h2d / (ms * 1e-3) / 1e9, "d2h_gbs_per_gpu": d2h / (ms * 1e-3) / 1e9,
+                "ceiling": ceiling, "pcie_gen5_x16_nominal_gbs_per_direction": 63.0}
+        link["frac_of_measured_bidirectional"] = ((link["h2d_gbs_per_gpu"] + link["d2h_gbs_per_gpu"]) /
+                                                  (2 * ceiling["both_each_gbs"]))
+        e2e = {"value": value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": ms}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": 1,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": WORKLOADS["c4"], "elements_per_step": total,
+                           "l2": "streamed chunks of 1 GiB per slot far exceed L2",
+                           "parallelism": f"tensors round-robin over {world} ranks" if world > 1 else "single"},
+                "roofline": {"bound": "host link", "achieved": link["h2d_gbs_per_gpu"] + link["d2h_gbs_per_gpu"],
+                             "peak": 2 * ceiling["both_each_gbs"], "unit": "GB/s",
+                             "frac": link["frac_of_measured_bidirectional"], "traffic": None,
+                             "peak_source": "pinned cudaMemcpyAsync both directions at once, same run"},
+                "link": link, "e2e": e2e, "cpu_baseline": None,
+                "gpu_launches": int(s1["kernel_launches"] - s0["kernel_launches"]),
+                "clocks": sampler.stop(t0, t1) if sampler else None}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -253,6 +359,9 @@ def main():
     state_dtype = torch.float32 if wl == "c2" else torch.bfloat16
     bytes_per_elem = 22 if wl == "c2" else 14
     start_step = 10 if wl == "c1" else START_STEP
+
+    if wl == "c4":
+        return run_c4(args, device, rank, world, warmup)
 
     # ---------------------------------------------------------------- resident step (value)
     # Every workload is a list of parameters in ONE group handed to create_zero_param_groups, so
@@ -344,6 +453,27 @@ def main():
                 "algorithmic_bytes": bytes_per_elem * per_rank, "kernel_ms": upd_ms,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 
+    # ---------------------------------------------------------------- ZeRO-2 reduce-scatter (N > 1)
+    rs_ms = None
+    if world > 1:
+        from ramtorch_b200.zero2 import reduce_gradients_now, setup_grad_sharding_hooks
+        for grp_list in rpgs[0].values():
+            for grp in grp_list:
+                for p in grp["params"]:
+                    p.requires_grad_(True)
+        setup_grad_sharding_hooks(rpgs[0], rank)   # flat gradient buffer, p.grad become views of it
+        for _ in range(2):
+            reduce_gradients_now(rpgs[0])
+        torch.cuda.synchronize(); dist.barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(5):
+            reduce_gradients_now(rpgs[0])
+        r1.record(); torch.cuda.synchronize()
+        t = torch.tensor([r0.elapsed_time(r1) / 5], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rs_ms = t.item()
+
     # ---------------------------------------------------------------- end to end from host memory
     e2e = None
     if not args.no_e2e and wl == "c2":
@@ -394,6 +524,11 @@ def main():
                "h2d_gbs": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs": d2h / (e2e_ms * 1e-3) / 1e9,
                "steps": args.e2e_steps, "chunk_elems": hopt.offload_chunk_elems,
                "ring_depth": hopt.offload_ring_depth}
+        if rank == 0:
+            del hopt, hst, hp_, hg
+            e2e["link_ceiling"] = link_ceiling(device)
+            e2e["frac_of_measured_bidirectional_link"] = ((e2e["h2d_gbs"] + e2e["d2h_gbs"]) /
+                                                          (2 * e2e["link_ceiling"]["both_each_gbs"]))
 
     base = None
     if rank == 0 and world == 1 and not args.no_cpu and wl == "c2":
@@ -414,7 +549,7 @@ def main():
                            "parallelism": f"zero1x{world}" if world > 1 else "single"},
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
-                "update_only_value": total_elems / (upd_ms * 1e-3), "host_ms_per_step": host_ms}
+                "t_reduce_scatter_ms": rs_ms, "host_ms_per_step": host_ms}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

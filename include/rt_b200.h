@@ -246,6 +246,9 @@ int rt_adamw_sr_multi_static(const rt_tensor_desc* tensors, int64_t count,
 typedef struct rt_offload_cfg {
   int64_t chunk_elems;  /* multiple of 8; 0 = default (128 Mi elements / 8) */
   int ring_depth;       /* 2..8; 0 = default 3 */
+  int defer_join;       /* 0: cuda_stream waits for this call's work before the call returns;
+                           1: it does not -- call rt_offload_join once after the last tensor, so
+                              that consecutive tensors overlap in the pipeline */
   void* staging;        /* device memory */
   int64_t staging_bytes;
 } rt_offload_cfg;
@@ -258,6 +261,10 @@ int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int64_t n,
                         int p_dtype, int g_dtype, int state_dtype,
                         const rt_hyper* hyper, uint64_t seed, uint32_t tensor_id,
                         const rt_offload_cfg* cfg, void* cuda_stream);
+
+/* Make cuda_stream wait for everything the streaming pipeline of the current device has been
+ * given so far (use with rt_offload_cfg.defer_join = 1). */
+int rt_offload_join(void* cuda_stream);
 
 /* Pin / unpin caller-owned host memory (cudaHostRegister) so the copy engines can stream it;
  * needed for shared-memory parameter storage that arrives unpinned in worker processes. */

@@ -47,8 +47,8 @@ class TensorDesc(ctypes.Structure):
 
 
 class OffloadCfg(ctypes.Structure):
-    _fields_ = [("chunk_elems", c_int64), ("ring_depth", c_int), ("staging", c_void_p),
-                ("staging_bytes", c_int64)]
+    _fields_ = [("chunk_elems", c_int64), ("ring_depth", c_int), ("defer_join", c_int),
+                ("staging", c_void_p), ("staging_bytes", c_int64)]
 
 
 MAX_PEERS = 15
@@ -86,6 +86,7 @@ _SIGNATURES = {
     "rt_adamw_sr_offload": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                     ctypes.POINTER(Hyper), c_uint64, c_uint32,
                                     ctypes.POINTER(OffloadCfg), c_void_p]),
+    "rt_offload_join": (c_int, [c_void_p]),
     "rt_host_register": (c_int, [c_void_p, c_int64]),
     "rt_host_unregister": (c_int, [c_void_p]),
     "rt_query_stats": (c_int, [ctypes.POINTER(Stats)]),

@@ -114,7 +114,11 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
   std::lock_guard<std::mutex> lock(g_pipe_mu);
   Pipe* pipe = nullptr;
   if (int rc = get_pipe(device, &pipe)) return rc;
-  const int64_t slot_bytes = need / depth;
+  // The ring's geometry comes from the staging buffer, not from this tensor: slots of
+  // staging_bytes / depth, so tensors of different sizes, dtypes and residency share one ring
+  // and follow each other without a drain.
+  const int64_t slot_bytes = cfg->staging ? (cfg->staging_bytes / depth) & ~(int64_t)255 : 0;
+  if (need / depth > slot_bytes) return fail(RT_E_CONFIG, "staging buffer too small: need " + std::to_string(need) + " bytes");
   if (pipe->staging != cfg->staging || pipe->slot_bytes != slot_bytes || pipe->depth != depth) {
     // new ring geometry: let everything that used the old one finish first
     RT_CUDA(cudaStreamSynchronize(pipe->out));
@@ -200,7 +204,22 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
     RT_CUDA(cudaEventRecord(pipe->out_done[slot], pipe->out));
   }
 
+  if (cfg->defer_join) return 0;
   // the caller's stream resumes when the last kernel and the last copy-out are done
+  RT_CUDA(cudaEventRecord(pipe->exit_run, pipe->run));
+  RT_CUDA(cudaEventRecord(pipe->exit_out, pipe->out));
+  RT_CUDA(cudaStreamWaitEvent(user, pipe->exit_run, 0));
+  RT_CUDA(cudaStreamWaitEvent(user, pipe->exit_out, 0));
+  return 0;
+}
+
+extern "C" int rt_offload_join(void* cuda_stream) {
+  int device = 0;
+  RT_CUDA(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(g_pipe_mu);
+  if (device < 0 || device >= 64 || g_pipes[device].device < 0) return 0;  // pipeline never used
+  Pipe* pipe = &g_pipes[device];
+  cudaStream_t user = (cudaStream_t)cuda_stream;
   RT_CUDA(cudaEventRecord(pipe->exit_run, pipe->run));
   RT_CUDA(cudaEventRecord(pipe->exit_out, pipe->out));
   RT_CUDA(cudaStreamWaitEvent(user, pipe->exit_run, 0));

@@ -303,8 +303,10 @@ class AdamW(Optimizer):
                         "rt_adamw_sr_multi")
                 launches += plan.launches
 
+        # one staging ring per device, sized for the largest streamed tensor of this step, so that
+        # all of them share its geometry and follow each other through the pipeline
+        jobs, ring_bytes = [], {}
         for index, pd, grad, ema, ema_sq, tid, hi in streamed:
-            used.add(index)
             host = [not t.is_cuda for t in (pd, grad, ema, ema_sq)]
             if not self._warned_pageable:
                 for t, h in zip((pd, grad, ema, ema_sq), host):
@@ -318,15 +320,23 @@ class AdamW(Optimizer):
             need = lib.rt_offload_staging_bytes(chunk, self.offload_ring_depth, *codes, *map(int, host))
             if need < 0:
                 N.check(int(need), "rt_offload_staging_bytes")
+            ring_bytes[index] = max(ring_bytes.get(index, 256 * self.offload_ring_depth), int(need))
+            jobs.append((index, pd, grad, ema, ema_sq, tid, hi, codes, chunk))
+        for index, pd, grad, ema, ema_sq, tid, hi, codes, chunk in jobs:
+            used.add(index)
             with torch.cuda.device(index):
-                staging = self._staging_for(index, max(int(need), 256))
-                cfg = N.OffloadCfg(chunk, self.offload_ring_depth, staging.data_ptr(), staging.numel())
+                staging = self._staging_for(index, ring_bytes[index])
+                cfg = N.OffloadCfg(chunk, self.offload_ring_depth, 1, staging.data_ptr(), staging.numel())
                 N.check(lib.rt_adamw_sr_offload(pd.data_ptr(), grad.data_ptr(), ema.data_ptr(),
                                                 ema_sq.data_ptr(), pd.numel(), *codes,
                                                 ctypes.byref(hyper_arr[hi]), seed, tid,
                                                 ctypes.byref(cfg), N.stream_ptr(index)),
                         "rt_adamw_sr_offload")
             launches += (pd.numel() + chunk - 1) // chunk
+        for index in {e[0] for e in streamed}:
+            # one join per device after the last tensor, so consecutive tensors overlap in the pipeline
+            with torch.cuda.device(index):
+                N.check(lib.rt_offload_join(N.stream_ptr(index)), "rt_offload_join")
 
         self._mark_pushed(resident, streamed)
         self.last_step_info = dict(launches=launches, resident=sum(map(len, resident.values())),

@@ -50,6 +50,18 @@ def finish_grad_sync() -> None:
                 _reduce_bucket(plan, bucket, plan.current_rank)
 
 
+def reduce_gradients_now(rank_param_groups) -> None:
+    """Reduce-scatter every flat gradient buffer of this dict right away, whether or not all
+    gradients have arrived (for loops that produce gradients outside autograd).  Collective:
+    every rank must call it."""
+    plan = plan_for(rank_param_groups)
+    if plan.current_rank is None:
+        raise RuntimeError("call setup_grad_sharding_hooks first")
+    for bucket in plan.buckets.values():
+        if bucket.gflat is not None:
+            _reduce_bucket(plan, bucket, plan.current_rank)
+
+
 def setup_grad_sharding_hooks(rank_param_groups, current_rank):
     """Register the gradient-reduction hooks for every parameter of every rank's groups.
 
