@@ -453,6 +453,13 @@ def main():
                 "algorithmic_bytes": bytes_per_elem * per_rank, "kernel_ms": upd_ms,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
 
+    redistribution = None
+    if world > 1:
+        from ramtorch_b200._shard_plan import plan_for
+        modes = sorted({str(bk.mode) for bk in plan_for(rpgs[0]).buckets.values()})
+        redistribution = {"push": "fused peer stores from the optimizer kernel + barrier",
+                          "gather": "NCCL all-gather"}.get(modes[0], modes[0]) if len(modes) == 1 else str(modes)
+
     # ---------------------------------------------------------------- ZeRO-2 reduce-scatter (N > 1)
     rs_ms = None
     if world > 1:
@@ -549,7 +556,8 @@ def main():
                            "parallelism": f"zero1x{world}" if world > 1 else "single"},
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
-                "t_reduce_scatter_ms": rs_ms, "host_ms_per_step": host_ms}
+                "t_reduce_scatter_ms": rs_ms, "zero1_redistribution": redistribution,
+                "host_ms_per_step": host_ms}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
