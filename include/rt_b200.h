@@ -90,6 +90,14 @@ typedef struct rt_hyper {
  * matters for the all-bf16 variant (three Philox calls per eight elements) that is otherwise
  * bound by instruction issue rather than HBM. */
 #define RT_HYPER_FAST_MATH 1u
+/* One Philox block per eight elements instead of three: the block of stream 0 also serves
+ * the moments, read two lanes further per stream -- element i of stream s takes draw
+ * ((i & 7) + 2*s) & 7 of the block of its group.  Each rounding still sees a uniform 16-bit
+ * draw and stays unbiased; what is given up is independence between the rounding of p[i],
+ * ema[i-2] and ema_squared[i-4] inside one group of eight.  (The reference shares one stream
+ * between ALL tensors of a step, adamw.py:206-218.)  Results remain bit-identical to the CPU
+ * checker run with the same flag.  Off by default; only matters when the moments are bf16. */
+#define RT_HYPER_SHARED_DRAWS 2u
 
 /* Fill an rt_hyper from the constructor-level values, in double precision, as
  * adamw.py:173-188 does.  Pure host arithmetic. */

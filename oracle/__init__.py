@@ -77,7 +77,7 @@ def num_threads() -> int:
     return int(lib().rto_num_threads())
 
 
-def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0) -> Hyper:
+def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, shared_draws=False) -> Hyper:
     """Per-step scalars exactly as adamw.py:173-188 forms them (Python doubles), each rounded
     once to fp32 where ATen would cast the Python scalar to the tensor's dtype."""
     beta1, beta2 = betas
@@ -96,6 +96,7 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0) -> Hyper:
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
+    h.flags = 2 if shared_draws else 0
     h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 

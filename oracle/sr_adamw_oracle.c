@@ -47,8 +47,18 @@ void rto_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t ou
 }
 
 /* The 16-bit draw of element i (index inside its tensor); include/rt_b200.h "Random bits". */
+static inline uint32_t draw16_at(uint64_t seed, uint32_t tensor_id, uint32_t step,
+                                 uint32_t stream, int64_t i);
+
+/* RT_HYPER_SHARED_DRAWS: every stream reads the block of stream 0, two lanes further per stream. */
 static inline uint32_t draw16(uint64_t seed, uint32_t tensor_id, uint32_t step,
-                              uint32_t stream, int64_t i) {
+                              uint32_t stream, int64_t i, int shared) {
+  if (!shared) return draw16_at(seed, tensor_id, step, stream, i);
+  return draw16_at(seed, tensor_id, step, 0, (i & ~(int64_t)7) | (((i & 7) + 2 * (int64_t)stream) & 7));
+}
+
+static inline uint32_t draw16_at(uint64_t seed, uint32_t tensor_id, uint32_t step,
+                                 uint32_t stream, int64_t i) {
   uint32_t ctr[4] = {(uint32_t)((uint64_t)i >> 3), tensor_id, step, stream};
   uint32_t key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
   uint32_t out[4];
@@ -62,7 +72,7 @@ void rto_draws(uint64_t seed, uint32_t tensor_id, uint32_t step, uint32_t stream
                int64_t index0, int64_t n, uint16_t* out) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i)
-    out[i] = (uint16_t)draw16(seed, tensor_id, step, stream, index0 + i);
+    out[i] = (uint16_t)draw16(seed, tensor_id, step, stream, index0 + i, 0);
 }
 
 /* ---------------------------------------------------------------- bit helpers */
@@ -143,10 +153,11 @@ int rto_adamw_sr(void* p, const void* g, void* m, void* v, int64_t n,
     if (f32_v) f32_v[i] = v1;
     int64_t gi_idx = index0 + i;
     uint32_t rp = 0, rm = 0, rv = 0;
-    if (sr_p) rp = rand_p ? rand_p[i] : draw16(seed, tensor_id, h->step, 0, gi_idx);
+    const int shared = (h->flags & RT_HYPER_SHARED_DRAWS) != 0;
+    if (sr_p) rp = rand_p ? rand_p[i] : draw16(seed, tensor_id, h->step, 0, gi_idx, shared);
     if (sr_s) {
-      rm = rand_m ? rand_m[i] : draw16(seed, tensor_id, h->step, 1, gi_idx);
-      rv = rand_v ? rand_v[i] : draw16(seed, tensor_id, h->step, 2, gi_idx);
+      rm = rand_m ? rand_m[i] : draw16(seed, tensor_id, h->step, 1, gi_idx, shared);
+      rv = rand_v ? rand_v[i] : draw16(seed, tensor_id, h->step, 2, gi_idx, shared);
     }
     store_from_f32(p, p_dtype, i, p1, rp);
     store_from_f32(m, state_dtype, i, m1, rm);

@@ -31,6 +31,7 @@ class Hyper(ctypes.Structure):
 
 
 HYPER_FAST_MATH = 1
+HYPER_SHARED_DRAWS = 2
 
 
 class Debug(ctypes.Structure):
@@ -119,7 +120,8 @@ def check(rc: int, what: str = "librt_b200") -> None:
         raise kind(f"{what} failed ({rc}): {msg}")
 
 
-def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math=False) -> Hyper:
+def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math=False,
+               shared_draws=False) -> Hyper:
     """The per-step scalars of ``adamw.py:173-188``: Python-double arithmetic written the way the
     reference writes it, then one rounding to fp32 each (what ATen does when a Python scalar
     meets an fp32 tensor)."""
@@ -137,7 +139,7 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
-    h.flags = HYPER_FAST_MATH if fast_math else 0
+    h.flags = (HYPER_FAST_MATH if fast_math else 0) | (HYPER_SHARED_DRAWS if shared_draws else 0)
     h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 

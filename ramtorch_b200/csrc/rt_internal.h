@@ -58,7 +58,7 @@ inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 // nblocks chunks, or they are null and `one`/`one_h` describe a single tensor.
 int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* chunks,
                  const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
-                 uint64_t seed, int64_t nblocks, cudaStream_t stream, bool fast,
+                 uint64_t seed, int64_t nblocks, cudaStream_t stream, uint32_t flags,
                  const PushTable* push);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);

@@ -116,12 +116,16 @@ class AdamW(Optimizer):
         fast_math: approximate square root and reciprocal in the parameter update (moments stay
             exact); results stay within 1e-6 relative of the exact update but are no longer
             bit-identical to the CPU checker (default False).
+        shared_draws: one Philox block per eight elements serves parameter and both moments
+            (rotated lanes) instead of three independent blocks; every rounding stays uniform and
+            unbiased and the result stays bit-identical to the checker run with the same flag
+            (default False; only matters for bf16 moments).
     """
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
                  centralization=0, chunk_size=64, dtype=torch.bfloat16, storage_device="cpu",
                  *, seed=0, offload_chunk_elems=1 << 24, offload_ring_depth=3, sync=True,
-                 fast_math=False):
+                 fast_math=False, shared_draws=False):
         if dtype not in N.DTYPE_CODE:
             raise ValueError(f"unsupported state dtype {dtype}: bf16, fp32 or fp16")
         if offload_chunk_elems <= 0 or offload_chunk_elems % 8:
@@ -142,6 +146,7 @@ class AdamW(Optimizer):
         self.offload_ring_depth = int(offload_ring_depth)
         self.sync = bool(sync)
         self.fast_math = bool(fast_math)
+        self.shared_draws = bool(shared_draws)
         self._plans = {}      # cuda device index -> _DevicePlan
         self._staging = {}    # cuda device index -> uint8 tensor
         self._row_scratch = {}  # cuda device index -> fp32 row means for centralization
@@ -246,7 +251,7 @@ class AdamW(Optimizer):
                     hi = hyper_index[key] = len(hyper_rows)
                     hyper_rows.append(N.make_hyper(group["lr"], group["betas"], group["eps"],
                                                    group["weight_decay"], state["step"],
-                                                   group["centralization"], self.fast_math))
+                                                   group["centralization"], self.fast_math, self.shared_draws))
                 ema, ema_sq = state["ema"], state["ema_squared"]
                 pd = p.data
                 if not pd.is_contiguous():
@@ -427,7 +432,7 @@ class AdamW(Optimizer):
         for gi, step in f["classes"]:
             g = groups[gi]
             rows.append(N.make_hyper(g["lr"], g["betas"], g["eps"], g["weight_decay"], step + 1,
-                                     g["centralization"], self.fast_math))
+                                     g["centralization"], self.fast_math, self.shared_draws))
         f["classes"] = [(gi, step + 1) for gi, step in f["classes"]]
         hyper_arr = (N.Hyper * len(rows))(*rows)
         gptrs = np.fromiter(map(torch.Tensor.data_ptr, grads), dtype=np.uint64, count=len(grads))

@@ -19,16 +19,17 @@ def setup_module(module):
     F = functional
 
 
-def _hyper_pair(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, wd=0.01, step=11):
+def _hyper_pair(lr=1e-4, betas=(0.9, 0.999), eps=1e-8, wd=0.01, step=11, shared=False):
     from ramtorch_b200 import _native as N
-    return N.make_hyper(lr, betas, eps, wd, step), oracle.make_hyper(lr, betas, eps, wd, step)
+    return (N.make_hyper(lr, betas, eps, wd, step, shared_draws=shared),
+            oracle.make_hyper(lr, betas, eps, wd, step, shared_draws=shared))
 
 
 def run_both(n, kp, kg, ks, *, seed=3, tensor_id=5, index0=0, step=11, wd=0.01, misalign=0,
-             inject=False, taps=False, data_seed=0):
+             inject=False, taps=False, data_seed=0, shared=False):
     """Run the CUDA kernel and the checker on the same seeded inputs; return both results."""
     p, g, m, v = synth(n, kp, kg, ks, data_seed)
-    hn, ho = _hyper_pair(step=step, wd=wd)
+    hn, ho = _hyper_pair(step=step, wd=wd, shared=shared)
     dev = torch.device("cuda")
 
     def dev_tensor(arr, kind):
@@ -330,3 +331,24 @@ def test_centralized_step_is_bit_exact_given_the_same_row_means(shape):
                     row_mean=means.cpu().numpy(), row_len=row_len if rows > 1 else 0)
     for t, want in zip((tp, tm, tv), (p, m, v)):
         assert bits_equal(to_numpy(t), want) == 0
+
+
+@pytest.mark.parametrize("kinds", [("bf16", "bf16", "bf16"), ("f32", "bf16", "bf16"), ("f16", "f32", "bf16"),
+                                   ("bf16", "bf16", "f32")])
+@pytest.mark.parametrize("n,misalign", [(100003, 0), (8200, 3), (5, 0)])
+def test_shared_draws_layout_is_bit_exact_with_checker(kinds, n, misalign):
+    """RT_HYPER_SHARED_DRAWS: one Philox block per eight elements, rotated per stream; vector,
+    scalar and tail paths must pick the same lanes as the checker."""
+    got, want, _, _ = run_both(n, *kinds, shared=True, misalign=misalign)
+    for a, b in zip(got, want):
+        assert bits_equal(a, b) == 0
+    # the debug kernel follows the same layout
+    got2, _, _, _ = run_both(n, *kinds, shared=True, misalign=misalign, taps=True)
+    for a, b in zip(got2, want):
+        assert bits_equal(a, b) == 0
+    if kinds[2] == "bf16":
+        # and it differs from the independent layout in the moments, not in the parameter
+        indep, _, _, _ = run_both(n, *kinds, shared=False, misalign=misalign)
+        assert bits_equal(got[0], indep[0]) == 0
+        if n > 1000:
+            assert bits_equal(got[1], indep[1]) > 0
