@@ -121,7 +121,7 @@ def cpu_baseline(seconds=12.0, sample_elems=1 << 26, warmup=1, steps=None):
     g = oracle.f32_to_bf16_bits_rn(normal(1e-3))
     m = normal(1e-3)
     v = np.abs(normal(1e-6))
-    threads = oracle.num_threads()
+    threads = oracle.use_all_cores()
     times, k = [], 0
     t_end = time.time() + seconds
     while True:
@@ -454,6 +454,25 @@ def main():
                 "frac": achieved / peak, "peak_source": which, "traffic": traffic,
                 "algorithmic_bytes": bytes_per_elem * per_rank, "kernel_ms": upd_ms,
                 "frac_of_nominal_8TBs": achieved / 8000.0}
+    if world > 1:
+        from ramtorch_b200._shard_plan import plan_for as _plan_for
+        if all(bk.mode == "push" for bk in _plan_for(rpgs[0]).buckets.values()):
+            # fused update + redistribution: the kernel also stores every updated bf16 parameter into
+            # the other ranks' buffers, so its target time is the slower of the HBM time and the
+            # NVLink time (bytes leaving this GPU / measured peer-copy rate per direction)
+            nvlink_peak = 770.0
+            egress = 2.0 * per_rank * (world - 1)
+            t_hbm = bytes_per_elem * per_rank / (peak * 1e9)
+            t_link = egress / (nvlink_peak * 1e9)
+            target = max(t_hbm, t_link)
+            roofline = {"bound": "nvlink" if t_link > t_hbm else "hbm",
+                        "achieved": egress / (upd_ms * 1e-3) / 1e9 if t_link > t_hbm else achieved,
+                        "peak": nvlink_peak if t_link > t_hbm else peak, "unit": "GB/s",
+                        "frac": target / (upd_ms * 1e-3), "traffic": None, "kernel_ms": upd_ms,
+                        "peak_source": "measured peer copy, 770 GB/s per direction per GPU"
+                                       if t_link > t_hbm else which,
+                        "nvlink_egress_bytes": egress, "hbm_algorithmic_bytes": bytes_per_elem * per_rank,
+                        "target_ms": target * 1e3}
 
     redistribution = None
     if world > 1:

@@ -69,12 +69,25 @@ def lib() -> ctypes.CDLL:
         L.rto_hyper_fill.argtypes = [ctypes.POINTER(Hyper)] + [ctypes.c_double] * 6 + [u32]
         L.rto_hyper_fill.restype = None
         L.rto_num_threads.restype = ctypes.c_int
+        L.rto_set_num_threads.argtypes = [ctypes.c_int]
+        L.rto_set_num_threads.restype = None
         _lib = L
     return _lib
 
 
 def num_threads() -> int:
     return int(lib().rto_num_threads())
+
+
+def use_all_cores() -> int:
+    """Let the timed baseline use every core this process may run on, whatever OMP_NUM_THREADS
+    says (launchers such as torchrun export OMP_NUM_THREADS=1 to every rank)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().rto_set_num_threads(n)
+    return num_threads()
 
 
 def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, shared_draws=False) -> Hyper:

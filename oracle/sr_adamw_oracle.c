@@ -188,6 +188,15 @@ void rto_hyper_fill(rt_hyper* out, double lr, double beta1, double beta2, double
   out->inv_bias_correction2_sqrt = (float)(1.0 / (double)out->bias_correction2_sqrt);
 }
 
+void rto_set_num_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int rto_num_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);
