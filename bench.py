@@ -267,8 +267,11 @@ def run_c4(args, device, rank, world, warmup):
         p.copy_(scratch.normal_(0, 0.02)); st["ema"].copy_(scratch.normal_(0, 1e-3))
         st["ema_squared"].copy_(scratch.normal_(0, 1e-6).abs_())
         st["step"] = START_STEP
-        p.grad = torch.empty(n_each, dtype=torch.bfloat16, pin_memory=True)
-        p.grad.copy_(scratch.normal_(0, 1e-3))
+        if args.grads_in_hbm:
+            p.rt_device_grad = torch.empty(n_each, dtype=torch.bfloat16, device=device).normal_(0, 1e-3)
+        else:
+            p.grad = torch.empty(n_each, dtype=torch.bfloat16, pin_memory=True)
+            p.grad.copy_(scratch.normal_(0, 1e-3))
     del scratch
     ceiling = link_ceiling(device) if rank == 0 else None
     steps = max(1, min(args.steps, 3))
@@ -309,7 +312,8 @@ def run_c4(args, device, rank, world, warmup):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": 1,
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOADS["c4"], "elements_per_step": total,
+                "config": {"workload": WORKLOADS["c4"] + ("; variant: gradients kept in HBM" if args.grads_in_hbm else ""),
+                           "elements_per_step": total,
                            "l2": "streamed chunks of 1 GiB per slot far exceed L2",
                            "parallelism": f"tensors round-robin over {world} ranks" if world > 1 else "single"},
                 "roofline": {"bound": "host link", "achieved": link["h2d_gbs_per_gpu"] + link["d2h_gbs_per_gpu"],
@@ -336,6 +340,8 @@ def main():
     ap.add_argument("--fast-math", action="store_true", help="approximate sqrt/reciprocal in p' (off by default)")
     ap.add_argument("--shared-draws", action="store_true",
                     help="one Philox block per eight elements for p, m and v (off by default)")
+    ap.add_argument("--grads-in-hbm", action="store_true",
+                    help="c4 only: gradients of the CPU parameters stay in HBM (p.rt_device_grad)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

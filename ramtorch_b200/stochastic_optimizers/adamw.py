@@ -36,6 +36,20 @@ from .. import _native as N
 from ..functional import sr_round_bf16_
 
 _PARAM_IDS_KEY = "rt_param_ids"
+DEVICE_GRAD_ATTR = "rt_device_grad"
+
+
+def _grad_of(p):
+    """The gradient ``step`` consumes.  PyTorch refuses a CUDA ``.grad`` on a CPU parameter, so a
+    producer that keeps the gradient of a CPU-resident parameter in HBM (instead of copying it to
+    host memory only for ``step`` to copy it back, ramtorch/modules/linear.py:416-427 ->
+    adamw.py:167) hands it over as ``p.rt_device_grad``; it takes precedence over ``p.grad`` for
+    CPU parameters and is ignored for CUDA parameters."""
+    if not p.is_cuda:
+        g = getattr(p, DEVICE_GRAD_ATTR, None)
+        if g is not None:
+            return g
+    return p.grad
 
 
 def copy_stochastic_(target: torch.Tensor, source: torch.Tensor, seed=0):
@@ -226,10 +240,11 @@ class AdamW(Optimizer):
         streamed = []   # (device index, p, grad, ema, ema_sq, tensor_id, hyper_index)
         hyper_rows, hyper_index = [], {}
         centered = {}   # device index -> {position in resident[index]: number of rows}
+        skipped_empty = False
         late = []
         for gi, group in enumerate(self.param_groups):
             for p in group["params"]:
-                grad = p.grad
+                grad = _grad_of(p)
                 if grad is None:
                     continue
                 if grad.is_sparse:
@@ -240,7 +255,7 @@ class AdamW(Optimizer):
 
         for gi, group in enumerate(self.param_groups):
             for p in group["params"]:
-                grad = p.grad
+                grad = _grad_of(p)
                 if grad is None:
                     continue
                 state = self.state[p]
@@ -254,6 +269,9 @@ class AdamW(Optimizer):
                                                    group["centralization"], self.fast_math, self.shared_draws))
                 ema, ema_sq = state["ema"], state["ema_squared"]
                 pd = p.data
+                if pd.numel() == 0:
+                    skipped_empty = True      # nothing to update; the step counter still advances
+                    continue
                 if not pd.is_contiguous():
                     raise ValueError("parameters must be contiguous for the in-place fused update")
                 if not grad.is_contiguous():
@@ -346,7 +364,7 @@ class AdamW(Optimizer):
         self._mark_pushed(resident, streamed)
         self.last_step_info = dict(launches=launches, resident=sum(map(len, resident.values())),
                                    streamed=len(streamed))
-        if len(resident) == 1 and not streamed and not self._keepalive and not centered:
+        if len(resident) == 1 and not streamed and not self._keepalive and not centered and not skipped_empty:
             self._remember_fast(next(iter(resident)), hyper_index)
         if self.sync:
             # results are visible to the host when step() returns (adamw.py:232)

@@ -352,3 +352,33 @@ def test_shared_draws_layout_is_bit_exact_with_checker(kinds, n, misalign):
         assert bits_equal(got[0], indep[0]) == 0
         if n > 1000:
             assert bits_equal(got[1], indep[1]) > 0
+
+
+def test_special_values_follow_ieee_like_the_checker():
+    """Zeros, denormals, infinities and NaNs in every input: wherever the fp32 update is a number the
+    CUDA result is bit-identical to the checker's; where it is a NaN both sides produce a NaN."""
+    from ramtorch_b200 import _native as N
+    specials = np.array([0x0000, 0x8000, 0x0001, 0x8001, 0x007F, 0x0080, 0x3F80, 0xBF80, 0x7F7F, 0xFF7F,
+                         0x7F80, 0xFF80, 0x7FC0, 0x3A83, 0x0400, 0x7E00], dtype=np.uint16)
+    grid = np.array(np.meshgrid(specials, specials, specials, specials, indexing="ij")).reshape(4, -1)
+    p, g, m, v = (np.ascontiguousarray(a) for a in grid)
+    v = v & 0x7FFF                                           # second moments are never negative
+    n = p.size
+    dev = torch.device("cuda")
+    tp, tg, tm, tv = (to_torch(a, "bf16", dev) for a in (p, g, m, v))
+    taps = tuple(torch.empty(n, dtype=torch.float32, device=dev) for _ in range(3))
+    hn, ho = _hyper_pair(step=3)
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, seed=1, tensor_id=1, taps=taps)
+    tp2, tg2, tm2, tv2 = (to_torch(a, "bf16", dev) for a in (p, g, m, v))
+    F.adamw_sr_flat_(tp2, tg2, tm2, tv2, hn, seed=1, tensor_id=1)      # production kernel
+    torch.cuda.synchronize()
+    po, mo, vo = p.copy(), m.copy(), v.copy()
+    f32 = oracle.adamw_sr(po, g, mo, vo, oracle.BF16, oracle.BF16, oracle.BF16, ho, seed=1, tensor_id=1, want_f32=True)
+    for tap, ref, out_dbg, out_prod, want in zip(taps, f32, (tp, tm, tv), (tp2, tm2, tv2), (po, mo, vo)):
+        got32 = tap.cpu().numpy()
+        nan = np.isnan(ref)
+        assert (np.isnan(got32) == nan).all()
+        assert bits_equal(got32[~nan], ref[~nan]) == 0
+        assert bits_equal(to_numpy(out_dbg)[~nan], want[~nan]) == 0
+        assert bits_equal(to_numpy(out_prod)[~nan], want[~nan]) == 0
+    assert nan.any() and (~nan).sum() > n // 4
