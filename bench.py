@@ -342,6 +342,10 @@ def main():
                     help="one Philox block per eight elements for p, m and v (off by default)")
     ap.add_argument("--grads-in-hbm", action="store_true",
                     help="c4 only: gradients of the CPU parameters stay in HBM (p.rt_device_grad)")
+    ap.add_argument("--with-grad-sync", action="store_true",
+                    help="N > 1: include the ZeRO-2 gradient reduction in every timed step")
+    ap.add_argument("--fused-grad-pull", action="store_true",
+                    help="N > 1: no reduce-scatter; the optimizer kernel sums the ranks' gradients over NVLink")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -406,7 +410,24 @@ def main():
         owned_elems = make_set(ragged_shapes(), 0)
     torch.cuda.synchronize()
 
+    grad_sync = world > 1 and (args.with_grad_sync or args.fused_grad_pull)
+    if grad_sync:
+        from ramtorch_b200.zero2 import reduce_gradients_now, setup_grad_sharding_hooks
+        if args.fused_grad_pull:
+            os.environ["RT_ZERO2_FUSED_PULL"] = "1"
+        for rpg in rpgs:
+            for grp_list in rpg.values():
+                for grp in grp_list:
+                    for p in grp["params"]:
+                        p.requires_grad_(True)
+            setup_grad_sharding_hooks(rpg, rank)   # flat gradient buffer; every p.grad becomes a view of it
+            from ramtorch_b200._shard_plan import plan_for as _pf
+            for bk in _pf(rpg).buckets.values():
+                bk.gflat.normal_(0, 1e-3)          # every rank holds a gradient for every parameter
+
     def one_step(k):
+        if grad_sync:
+            reduce_gradients_now(rpgs[k % len(rpgs)])
         steppers[k % len(steppers)].step()
 
     def redistribute(k):
@@ -489,7 +510,7 @@ def main():
 
     # ---------------------------------------------------------------- ZeRO-2 reduce-scatter (N > 1)
     rs_ms = None
-    if world > 1:
+    if world > 1 and not grad_sync:
         from ramtorch_b200.zero2 import reduce_gradients_now, setup_grad_sharding_hooks
         for grp_list in rpgs[0].values():
             for grp in grp_list:
@@ -585,6 +606,10 @@ def main():
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
                 "t_reduce_scatter_ms": rs_ms, "zero1_redistribution": redistribution,
+                "zero2_reduction": (None if world == 1 else
+                                    "inside t_update: fused peer loads in the optimizer kernel" if args.fused_grad_pull else
+                                    "inside t_update: NCCL reduce-scatter before the kernel" if grad_sync else
+                                    "outside the timed step (t_reduce_scatter_ms measured separately)"),
                 "host_ms_per_step": host_ms}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -210,6 +210,26 @@ typedef struct rt_push {
 int rt_plan_set_push(rt_plan* plan, const rt_push* push);
 
 /*
+ * ZeRO-2 fused reduction (replaces the per-tensor dist.reduce of zero2.py:27-57 for the tensors
+ * this rank owns).  `local_base`/`bytes` describe a gradient region of this GPU that every
+ * rank keeps at the same layout; base[r] is rank r's copy as mapped into this process, in rank
+ * order, this rank's own included.  While set, every rt_adamw_sr_multi of the plan takes, for
+ * each tensor whose gradient pointer lies inside the region, g = ((g_0 + g_1) + ...) + g_{n-1}
+ * (fp32, rank order, plain peer loads) instead of the local gradient, so no reduce-scatter pass
+ * is needed and the sum is not rounded to the gradient dtype.  The caller orders the launch
+ * after every rank has finished writing its gradients, and the next writes after every rank's
+ * launch (barrier-like collectives on the same streams).  pull == NULL or n_ranks == 0 clears it.
+ */
+typedef struct rt_pull {
+  const void* local_base;
+  int64_t bytes;
+  int n_ranks;
+  int self_rank;        /* index of this rank in base[] */
+  const void* base[RT_MAX_PEERS + 1];
+} rt_pull;
+int rt_plan_set_pull(rt_plan* plan, const rt_pull* pull);
+
+/*
  * Multi-tensor step for callers that must not allocate.  No counterpart in the reference.
  *
  * rt_plan_create keeps its tensor, chunk and hyper-parameter tables in memory it obtains from

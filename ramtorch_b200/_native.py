@@ -60,6 +60,11 @@ class Push(ctypes.Structure):
                 ("peer_base", c_void_p * MAX_PEERS)]
 
 
+class Pull(ctypes.Structure):
+    _fields_ = [("local_base", c_void_p), ("bytes", c_int64), ("n_ranks", c_int), ("self_rank", c_int),
+                ("base", c_void_p * (MAX_PEERS + 1))]
+
+
 class Stats(ctypes.Structure):
     _fields_ = [("kernel_launches", c_uint64), ("h2d_bytes", c_uint64), ("d2h_bytes", c_uint64),
                 ("h2d_copies", c_uint64), ("d2h_copies", c_uint64)]
@@ -81,6 +86,7 @@ _SIGNATURES = {
     "rt_plan_launches": (c_int, [c_void_p]),
     "rt_adamw_sr_multi": (c_int, [c_void_p, ctypes.POINTER(Hyper), c_int, c_uint64, c_void_p]),
     "rt_plan_set_push": (c_int, [c_void_p, ctypes.POINTER(Push)]),
+    "rt_plan_set_pull": (c_int, [c_void_p, ctypes.POINTER(Pull)]),
     "rt_adamw_sr_multi_static": (c_int, [ctypes.POINTER(TensorDesc), c_int64, ctypes.POINTER(Hyper), c_int,
                                          c_uint64, c_void_p]),
     "rt_offload_staging_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),

@@ -49,6 +49,11 @@ class Bucket:
         self.pushed = False                  # set by the optimizer after a pushing launch
         self.mode = None                     # None (undecided) | "push" | "gather"
         self.checks = 0
+        # fused gradient reduction: `gflat` is peer-mapped and the optimizer kernel sums the
+        # ranks' copies itself instead of a reduce-scatter pass
+        self.gpeer_ptrs: Optional[List[int]] = None
+        self.gsymm = None
+        self.grads_written = False           # a backward wrote gradients since the last barrier
 
     def rank_segment(self, buf: torch.Tensor, rank: int) -> torch.Tensor:
         return buf[rank * self.segment:(rank + 1) * self.segment]
@@ -173,13 +178,24 @@ class ShardPlan:
                     p.data = view
         self.flattened = True
 
-    def attach_grad_buffers(self) -> None:
+    def attach_grad_buffers(self, fused_pull: bool = False) -> None:
         """Allocate the flat gradient buffers and make every ``p.grad`` a view so that autograd
-        accumulates straight into them."""
+        accumulates straight into them.  With ``fused_pull`` (and a peer-mapped parameter buffer)
+        the gradient buffer is peer-mapped too, for the optimizer kernel to read every rank's copy."""
         for b in self.buckets.values():
             if b.gflat is not None:
                 continue
-            b.gflat = torch.zeros(b.segment * self.world_size, dtype=b.dtype, device=b.device)
+            n = b.segment * self.world_size
+            if fused_pull and b.peer_ptrs is not None:
+                import torch.distributed._symmetric_memory as symm
+                b.gflat = symm.empty(n, dtype=b.dtype, device=b.device)
+                handle = symm.rendezvous(b.gflat, dist.group.WORLD)
+                b.gpeer_ptrs = [int(q) for q in handle.buffer_ptrs]
+                b.gsymm = handle
+                b.gflat.zero_()
+                _PULL_BUCKETS.setdefault(b.device.index, []).append(b)
+            else:
+                b.gflat = torch.zeros(n, dtype=b.dtype, device=b.device)
             b.grad_views = []
             b.expected = 0
             for p, off in zip(b.params, b.offset):
@@ -194,6 +210,19 @@ class ShardPlan:
 
 _PLANS: Dict[int, tuple] = {}
 _PUSH_BUCKETS: Dict[int, List[Bucket]] = {}   # cuda device index -> buckets with peer-mapped buffers
+_PULL_BUCKETS: Dict[int, List[Bucket]] = {}   # cuda device index -> buckets with peer-mapped gradients
+
+
+def pull_bucket_for(device_index: int, grad_ptrs) -> Optional[Bucket]:
+    """The peer-mapped gradient bucket on ``device_index`` that holds most of the given addresses."""
+    best, best_hits = None, 0
+    for b in _PULL_BUCKETS.get(device_index, []):
+        lo = b.gflat.data_ptr()
+        hi = lo + b.gflat.numel() * b.gflat.element_size()
+        hits = sum(1 for q in grad_ptrs if q is not None and lo <= q < hi)
+        if hits > best_hits:
+            best, best_hits = b, hits
+    return best
 
 
 def all_push_buckets() -> List[Bucket]:

@@ -98,7 +98,7 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
   if ((chunk & 7) || depth < 2 || depth > kMaxDepth) return fail(RT_E_CONFIG, "chunk_elems must be a multiple of 8 and ring_depth in 2..8");
   if (n == 0) return 0;
 
-  bool hp, hg, hm, hv;
+  bool hp = false, hg = false, hm = false, hv = false;
   if (int rc = is_host_ptr(p, &hp)) return rc;
   if (int rc = is_host_ptr(g, &hg)) return rc;
   if (int rc = is_host_ptr(m, &hm)) return rc;

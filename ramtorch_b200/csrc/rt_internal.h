@@ -51,6 +51,22 @@ struct Stats {
 };
 Stats& stats();
 
+// Peer copies of a shared gradient region (kernel argument; n == 0 disables): base[r] is the
+// region in rank r's memory as mapped here, in rank order, this rank's own copy included.
+struct PullTable {
+  const char* local;
+  int64_t bytes;
+  int n;                      // number of ranks
+  int self;                   // this rank's index (its copy is read from t.g directly)
+  int staged;                 // set by the launcher: peers' words are staged through shared memory
+  const char* base[RT_MAX_PEERS + 1];
+};
+
+struct PeerTables {
+  PushTable push;
+  PullTable pull;
+};
+
 inline int dtype_size(int d) { return d == RT_F32 ? 4 : 2; }
 inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 
@@ -59,7 +75,7 @@ inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* chunks,
                  const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
                  uint64_t seed, int64_t nblocks, cudaStream_t stream, uint32_t flags,
-                 const PushTable* push);
+                 const PeerTables* peers);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
 int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,

@@ -95,6 +95,20 @@ class _DevicePlan:
             for k, q in enumerate(peers):
                 push.peer_base[k] = q
             N.check(N.lib().rt_plan_set_push(self.handle, ctypes.byref(push)), "rt_plan_set_push")
+        # ZeRO-2: when the gradients live in a peer-mapped flat buffer, let the kernel sum the
+        # ranks' copies itself
+        from .._shard_plan import pull_bucket_for
+        self.pull_bucket = pull_bucket_for(device_index, [d.g for d in descs])
+        if self.pull_bucket is not None:
+            b = self.pull_bucket
+            pull = N.Pull()
+            pull.local_base = b.gflat.data_ptr()
+            pull.bytes = b.gflat.numel() * b.gflat.element_size()
+            pull.n_ranks = len(b.gpeer_ptrs)
+            pull.self_rank = b.rank
+            for k, q in enumerate(b.gpeer_ptrs):
+                pull.base[k] = q
+            N.check(N.lib().rt_plan_set_pull(self.handle, ctypes.byref(pull)), "rt_plan_set_pull")
 
     def close(self):
         if self.handle:
@@ -413,12 +427,18 @@ class AdamW(Optimizer):
             emas=[st["ema"] for st in states], ema_sqs=[st["ema_squared"] for st in states],
             p_ptrs=list(map(torch.Tensor.data_ptr, with_grad)),
             g_dtypes=[p.grad.dtype for p in with_grad],
-            classes=[key for key, _ in classes], n_groups=len(self.param_groups))
+            classes=[key for key, _ in classes], n_groups=len(self.param_groups),
+            zero_buffers=self._zero_buffer_count(index))
+
+    @staticmethod
+    def _zero_buffer_count(index):
+        from .._shard_plan import _PULL_BUCKETS, _PUSH_BUCKETS
+        return len(_PUSH_BUCKETS.get(index, ())), len(_PULL_BUCKETS.get(index, ()))
 
     def _step_fast(self, lib) -> bool:
         f = self._fast
         groups = self.param_groups
-        if len(groups) != f["n_groups"]:
+        if len(groups) != f["n_groups"] or f["zero_buffers"] != self._zero_buffer_count(f["index"]):
             return False
         all_params = list(chain.from_iterable(g["params"] for g in groups))
         if list(map(id, all_params)) != f["all_ids"]:
@@ -492,9 +512,12 @@ class AdamW(Optimizer):
 
     def _plan_for(self, index, entries, row_info=None) -> _DevicePlan:
         row_info = row_info or {}
+        from .._shard_plan import _PULL_BUCKETS, _PUSH_BUCKETS
         signature = [(pd.data_ptr(), ema.data_ptr(), ema_sq.data_ptr(), pd.numel(), pd.dtype,
                       grad.dtype, ema.dtype, tid, hi, row_info.get(k))
                      for k, (pd, grad, ema, ema_sq, tid, hi) in enumerate(entries)]
+        # peer-mapped ZeRO buffers that appear after the plan was built must be picked up
+        signature.append((len(_PUSH_BUCKETS.get(index, ())), len(_PULL_BUCKETS.get(index, ()))))
         plan = self._plans.get(index)
         if plan is not None and plan.signature == signature:
             return plan

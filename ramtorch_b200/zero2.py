@@ -14,6 +14,7 @@ gradients are produced and consumed tensor by tensor inside ``Linear``'s backwar
 """
 from __future__ import annotations
 
+import os
 import weakref
 
 import torch
@@ -32,6 +33,13 @@ def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int) -> None:
     bucket.ready = 0
     if plan.world_size == 1 or not dist.is_initialized():
         return
+    if bucket.gpeer_ptrs is not None:
+        # fused reduction: the optimizer kernel will read every rank's copy itself; all that is
+        # needed here is that no rank starts reading before every rank has finished writing
+        if bucket.grads_written:
+            bucket.grads_written = False
+            dist.all_reduce(_barrier_token(bucket))
+        return
     mine = bucket.rank_segment(bucket.gflat, rank)
     work = dist.reduce_scatter_tensor(mine, bucket.gflat, op=dist.ReduceOp.SUM, async_op=True)
     work.wait()   # orders the current stream after the collective; the host does not block on NCCL
@@ -40,13 +48,20 @@ def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int) -> None:
     bucket.gflat[hi:].zero_()
 
 
+def _barrier_token(bucket: Bucket) -> torch.Tensor:
+    tok = getattr(bucket, "_token", None)
+    if tok is None:
+        tok = bucket._token = torch.zeros(1, dtype=torch.int32, device=bucket.device)
+    return tok
+
+
 def finish_grad_sync() -> None:
     """Reduce any bucket that received only part of its gradients in the last backward (unused
     parameters).  ``AdamW.step`` calls this first; every rank must call it the same number of
     times, as with any collective."""
     for plan in list(_ACTIVE_PLANS):
         for bucket in plan.buckets.values():
-            if bucket.gflat is not None and bucket.ready > 0:
+            if bucket.gflat is not None and (bucket.ready > 0 or bucket.grads_written):
                 _reduce_bucket(plan, bucket, plan.current_rank)
 
 
@@ -59,6 +74,7 @@ def reduce_gradients_now(rank_param_groups) -> None:
         raise RuntimeError("call setup_grad_sharding_hooks first")
     for bucket in plan.buckets.values():
         if bucket.gflat is not None:
+            bucket.grads_written = True
             _reduce_bucket(plan, bucket, plan.current_rank)
 
 
@@ -78,7 +94,11 @@ def setup_grad_sharding_hooks(rank_param_groups, current_rank):
     plan.current_rank = current_rank
     plan.verify_across_ranks()
     plan.flatten_params()
-    plan.attach_grad_buffers()
+    # RT_ZERO2_FUSED_PULL=1: no reduce-scatter at all -- the owners' optimizer kernel sums the ranks'
+    # gradient copies over NVLink while it updates (fp32 accumulation in rank order).  The owner's
+    # p.grad then stays the LOCAL gradient; code that inspects reduced gradients between backward
+    # and step (gradient clipping by global norm, logging) needs the default mode.
+    plan.attach_grad_buffers(fused_pull=os.environ.get("RT_ZERO2_FUSED_PULL", "0") == "1")
     _ACTIVE_PLANS.add(plan)
 
     def make_flat_hook(bucket: Bucket, index: int):
@@ -93,8 +113,12 @@ def setup_grad_sharding_hooks(rank_param_groups, current_rank):
                     view.copy_(grad)
                 param.grad = view
             bucket.ready += 1
+            bucket.grads_written = True
             if bucket.ready >= bucket.expected:
-                _reduce_bucket(plan, bucket, current_rank)
+                if bucket.gpeer_ptrs is not None:
+                    bucket.ready = 0          # fused reduction: the barrier waits for optimizer.step()
+                else:
+                    _reduce_bucket(plan, bucket, current_rank)
 
         return hook
 

@@ -22,8 +22,10 @@ def _params(device):
     return [torch.nn.Parameter((torch.randn(s, generator=g) * 0.02).bfloat16().to(device)) for s in SHAPES]
 
 
-def _grad(step, rank, k, shape):
+def _grad(step, rank, k, shape, exact=True):
     g = torch.Generator().manual_seed(1000 * step + 10 * rank + k)
+    if not exact:
+        return (torch.randn(shape, generator=g) * 1e-3).bfloat16()
     # multiples of 2^-14 with few significant bits: sums of up to 8 ranks are exact in bf16, so the
     # order in which NCCL adds them cannot matter
     return (torch.randint(-8, 9, shape, generator=g).float() * 2.0 ** -14).bfloat16()
@@ -34,9 +36,11 @@ def _groups(params):
             {"params": [p for p in params if p.dim() > 1]}]
 
 
-def _worker(rank, world, port, out, fused):
+def _worker(rank, world, port, out, mode, exact):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    fused = mode != "all-gather"
     os.environ["RT_ZERO_FUSED_PUSH"] = "1" if fused else "0"
+    os.environ["RT_ZERO2_FUSED_PULL"] = "1" if mode == "peer-push+grad-pull" else "0"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -50,7 +54,7 @@ def _worker(rank, world, port, out, fused):
         opt = AdamW(rpg[rank], dtype=torch.bfloat16, storage_device=dev, seed=21, **HP)
         for step in range(STEPS):
             # a "backward": every parameter receives this rank's gradient through autograd
-            loss = sum((p * _grad(step, rank, k, p.shape).to(dev)).sum() for k, p in enumerate(params))
+            loss = sum((p * _grad(step, rank, k, p.shape, exact).to(dev)).sum() for k, p in enumerate(params))
             loss.backward()
             opt.step()
             broadcast_zero_params(rpg)
@@ -60,6 +64,8 @@ def _worker(rank, world, port, out, fused):
         from ramtorch_b200._shard_plan import plan_for
         modes = sorted({str(b.mode) for b in plan_for(rpg).buckets.values()})
         assert modes == (["push"] if fused else ["None"]), modes
+        pulls = {b.gpeer_ptrs is not None for b in plan_for(rpg).buckets.values()}
+        assert pulls == {mode == "peer-push+grad-pull"}
         out.put((rank, "ok", [p.detach().float().cpu() for p in params]))
     except Exception as e:
         import traceback
@@ -68,22 +74,31 @@ def _worker(rank, world, port, out, fused):
         dist.destroy_process_group()
 
 
-def _single_process(world):
+def _single_process(world, exact=True, fp32_sum=False):
+    """The same optimisation in one process on the summed gradients.  ``fp32_sum``: the sum is kept
+    in fp32, accumulated in rank order -- what the fused reduction computes; otherwise it is rounded
+    to bf16 like an NCCL reduction of bf16 buffers."""
     from ramtorch_b200 import AdamW
     dev = torch.device("cuda", 0)
     params = _params(dev)
+    if fp32_sum:
+        for p in params:
+            p.grad_dtype = None
     opt = AdamW(_groups(params), dtype=torch.bfloat16, storage_device=dev, seed=21, **HP)
     for step in range(STEPS):
         for k, p in enumerate(params):
-            total = sum(_grad(step, r, k, p.shape).float() for r in range(world))
-            p.grad = total.bfloat16().to(dev)
+            total = _grad(step, 0, k, p.shape, exact).float()
+            for r in range(1, world):
+                total = total + _grad(step, r, k, p.shape, exact).float()
+            p.grad = (total if fp32_sum else total.bfloat16()).to(dev)
         opt.step()
     return [p.detach().float().cpu() for p in params]
 
 
-@pytest.mark.parametrize("fused", [True, False], ids=["peer-push", "all-gather"])
+@pytest.mark.parametrize("mode,exact", [("peer-push", True), ("all-gather", True), ("peer-push+grad-pull", True),
+                                        ("peer-push+grad-pull", False)])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_zero_loop_matches_single_process(world, fused):
+def test_zero_loop_matches_single_process(world, mode, exact):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
@@ -91,13 +106,13 @@ def test_zero_loop_matches_single_process(world, fused):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    procs = [ctx.Process(target=_worker, args=(r, world, port, out, fused)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out, mode, exact)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted((out.get() for _ in procs), key=lambda r: r[0])
     for p in procs:
         p.join(timeout=120)
-    want = _single_process(world)
+    want = _single_process(world, exact, fp32_sum=(mode == "peer-push+grad-pull"))
     for rank, status, payload in results:
         assert status == "ok", f"rank {rank}: {payload}"
         for k, (a, b) in enumerate(zip(payload, want)):
