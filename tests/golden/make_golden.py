@@ -191,7 +191,9 @@ def gen_zero1(zero1):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/RamTorch")
+    root = sys.argv[1]
     ref, zero1 = load_reference(root)
     gen_sr(ref)
     for i, (name, spec) in enumerate(STEP_CASES.items()):
