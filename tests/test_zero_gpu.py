@@ -53,9 +53,15 @@ def _worker(rank, world, port, out, mode, exact):
         setup_grad_sharding_hooks(rpg, rank)
         opt = AdamW(rpg[rank], dtype=torch.bfloat16, storage_device=dev, seed=21, **HP)
         for step in range(STEPS):
-            # a "backward": every parameter receives this rank's gradient through autograd
-            loss = sum((p * _grad(step, rank, k, p.shape, exact).to(dev)).sum() for k, p in enumerate(params))
-            loss.backward()
+            # a "backward": every parameter receives this rank's gradient through autograd; on odd
+            # steps in two micro-batches (gradient accumulation) whose halves add up exactly
+            grads = [_grad(step, rank, k, p.shape, exact).to(dev) for k, p in enumerate(params)]
+            if step % 2 == 1 and exact:
+                halves = [(g * 0.5, g - g * 0.5) for g in grads]      # powers of two: exact in bf16
+                for part in (0, 1):
+                    sum((p * h[part]).sum() for p, h in zip(params, halves)).backward()
+            else:
+                sum((p * g).sum() for p, g in zip(params, grads)).backward()
             opt.step()
             broadcast_zero_params(rpg)
             for p in params:
