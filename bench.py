@@ -260,7 +260,7 @@ def run_c4(args, device, rank, world, warmup):
         mine = mine[:-1]
     params = [torch.empty(n_each, dtype=torch.bfloat16, pin_memory=True) for _ in mine]
     opt = AdamW(params, dtype=torch.bfloat16, storage_device="cpu", seed=0, offload_chunk_elems=n_each,
-                offload_ring_depth=2, fast_math=args.fast_math, shared_draws=args.shared_draws, **HP)
+                offload_ring_depth=2, fast_math=args.fast_math, shared_draws=not args.independent_draws, **HP)
     scratch = torch.empty(n_each, dtype=torch.float32, device=device)
     for p in params:
         st = opt.state[p]
@@ -338,8 +338,9 @@ def main():
     ap.add_argument("--elems", type=int, default=ELEMS_PER_GPU, help="elements per GPU for c2/bf16 (default 2^30)")
     ap.add_argument("--e2e-steps", type=int, default=4)
     ap.add_argument("--fast-math", action="store_true", help="approximate sqrt/reciprocal in p' (off by default)")
-    ap.add_argument("--shared-draws", action="store_true",
-                    help="one Philox block per eight elements for p, m and v (off by default)")
+    ap.add_argument("--independent-draws", action="store_true",
+                    help="three independent Philox blocks per eight elements instead of one shared block "
+                         "(AdamW(shared_draws=False)); only matters for bf16 moments")
     ap.add_argument("--grads-in-hbm", action="store_true",
                     help="c4 only: gradients of the CPU parameters stay in HBM (p.rt_device_grad)")
     ap.add_argument("--with-grad-sync", action="store_true",
@@ -386,7 +387,7 @@ def main():
         rpg = create_zero_param_groups([{"params": params}], world)
         owned = rpg[rank][0]["params"]
         opt = AdamW(rpg[rank], dtype=state_dtype, storage_device=device, seed=seed, sync=False,
-                    fast_math=args.fast_math, shared_draws=args.shared_draws, **HP)
+                    fast_math=args.fast_math, shared_draws=not args.independent_draws, **HP)
         for p in owned:
             p.grad = torch.empty_like(p).normal_(0, 1e-3)
             st = opt.state[p]
@@ -601,7 +602,7 @@ def main():
                 "dtype": "f32", "data": "synthetic",
                 "config": {"workload": label, "elements_per_step": total_elems, "l2": l2,
                            "math": "fast (approx sqrt/rcp in p')" if args.fast_math else "exact (IEEE sqrt/div)",
-                           "draws": "one Philox block shared by p, m, v" if args.shared_draws else "independent Philox blocks",
+                           "draws": "independent Philox blocks" if args.independent_draws else "one Philox block shared by p, m, v",
                            "parallelism": f"zero1x{world}" if world > 1 else "single"},
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,

@@ -96,7 +96,8 @@ typedef struct rt_hyper {
  * draw and stays unbiased; what is given up is independence between the rounding of p[i],
  * ema[i-2] and ema_squared[i-4] inside one group of eight.  (The reference shares one stream
  * between ALL tensors of a step, adamw.py:206-218.)  Results remain bit-identical to the CPU
- * checker run with the same flag.  Off by default; only matters when the moments are bf16. */
+ * checker run with the same flag.  Only matters when the moments are bf16.  (The Python AdamW
+ * sets it unless told otherwise; at this ABI nothing is set by default.) */
 #define RT_HYPER_SHARED_DRAWS 2u
 
 /* Fill an rt_hyper from the constructor-level values, in double precision, as

@@ -32,7 +32,8 @@ def make_grads(shapes, dtype, seed):
 class Mirror:
     """The same optimisation carried out by the CPU checker, tensor by tensor."""
 
-    def __init__(self, params, state_dtype, seed, ids=None, **hp):
+    def __init__(self, params, state_dtype, seed, ids=None, shared_draws=True, **hp):
+        self.shared_draws = shared_draws      # AdamW's default
         self.p = [to_numpy(p) for p in params]
         self.kp = [KIND[p.dtype] for p in params]
         self.ks = KIND[state_dtype]
@@ -48,7 +49,8 @@ class Mirror:
             if k in skip:
                 continue
             self.step[k] += 1
-            h = oracle.make_hyper(self.hp["lr"], self.hp["betas"], self.hp["eps"], self.hp["weight_decay"], self.step[k])
+            h = oracle.make_hyper(self.hp["lr"], self.hp["betas"], self.hp["eps"], self.hp["weight_decay"], self.step[k],
+                                  shared_draws=self.shared_draws)
             oracle.adamw_sr(self.p[k], to_numpy(g), self.m[k], self.v[k], CODE[self.kp[k]], CODE[KIND[g.dtype]],
                             CODE[self.ks], h, seed=self.seed, tensor_id=self.ids[k])
 
@@ -67,12 +69,13 @@ def check(opt, params, mirror):
         assert st["ema"].shape == p.shape and st["ema_squared"].shape == p.shape
 
 
+@pytest.mark.parametrize("shared", [True, False], ids=["shared-draws", "independent-draws"])
 @pytest.mark.parametrize("state_dtype", [torch.bfloat16, torch.float32])
-def test_resident_multi_tensor_steps(state_dtype):
+def test_resident_multi_tensor_steps(state_dtype, shared):
     from ramtorch_b200 import AdamW
     params = make_params(SHAPES, torch.bfloat16, "cuda")
-    opt = AdamW(params, dtype=state_dtype, storage_device="cuda", seed=11, **HP)
-    mirror = Mirror(params, state_dtype, 11, **HP)
+    opt = AdamW(params, dtype=state_dtype, storage_device="cuda", seed=11, shared_draws=shared, **HP)
+    mirror = Mirror(params, state_dtype, 11, shared_draws=shared, **HP)
     for s in range(4):
         grads = make_grads(SHAPES, torch.bfloat16, s)
         skip = {2} if s == 1 else set()   # a parameter without a gradient is skipped, its step stays
