@@ -184,7 +184,7 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
     t.flags = vec_flag(t.p, t.g, t.m, t.v);
     if (int rc = launch_adamw(p_dtype, g_dtype, state_dtype, nullptr, nullptr, nullptr, t, *hyper, seed,
                               (len + kChunkElems - 1) / kChunkElems, pipe->run,
-                              hyper->flags, nullptr))
+                              hyper->flags, nullptr, nullptr))
       return rc;
     RT_CUDA(cudaEventRecord(pipe->run_done[slot], pipe->run));
 

@@ -67,6 +67,12 @@ struct PeerTables {
   PullTable pull;
 };
 
+// Hyper-parameter rows passed by value with a launch.
+constexpr int kPackRows = 4;
+struct HyperPack {
+  rt_hyper rows[kPackRows];
+};
+
 inline int dtype_size(int d) { return d == RT_F32 ? 4 : 2; }
 inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 
@@ -75,7 +81,7 @@ inline bool dtype_ok(int d) { return d >= RT_BF16 && d <= RT_F16; }
 int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* chunks,
                  const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
                  uint64_t seed, int64_t nblocks, cudaStream_t stream, uint32_t flags,
-                 const PeerTables* peers);
+                 const PeerTables* peers, const HyperPack* pack);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
 int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,

@@ -312,3 +312,50 @@ def test_empty_and_zero_dim_parameters():
             p.grad = g.cuda()
         opt.step(); mirror.apply(grads)
         check(opt, params, mirror)
+
+
+def test_step_hooks_and_lr_schedulers_keep_working():
+    """step() bypasses torch's per-call profiler wrapper when nothing is registered; hooks, LR
+    schedulers and the profiler range must behave as with any torch optimizer."""
+    from ramtorch_b200 import AdamW
+    p = make_params([(1000,)], torch.bfloat16, "cuda")[0]
+    opt = AdamW([p], dtype=torch.bfloat16, storage_device="cuda", **HP)
+    sched = torch.optim.lr_scheduler.StepLR(opt, step_size=1, gamma=0.5)
+    mirror = Mirror([p], torch.bfloat16, 0, **HP)
+    seen = []
+    h1 = opt.register_step_pre_hook(lambda o, a, k: seen.append("pre"))
+    h2 = opt.register_step_post_hook(lambda o, a, k: seen.append("post"))
+    for s in range(3):
+        g = make_grads([(1000,)], torch.bfloat16, s)
+        p.grad = g[0].cuda()
+        mirror.hp["lr"] = opt.param_groups[0]["lr"]
+        opt.step(); sched.step()
+        mirror.apply(g)
+        check(opt, [p], mirror)
+    assert seen == ["pre", "post"] * 3
+    assert abs(opt.param_groups[0]["lr"] - HP["lr"] * 0.125) < 1e-12
+    h1.remove(); h2.remove()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
+        p.grad = make_grads([(1000,)], torch.bfloat16, 9)[0].cuda()
+        opt.step()
+    assert any("Optimizer.step#AdamW.step" in e.key for e in prof.key_averages())
+    assert seen == ["pre", "post"] * 3
+
+
+def test_more_hyper_rows_than_ride_along_with_a_launch():
+    """Up to four (group, step) rows travel as kernel arguments; more go through the device table."""
+    from ramtorch_b200 import AdamW
+    shapes = [(300,), (4100,), (17,), (9000,), (64, 3), (2048,)]
+    params = make_params(shapes, torch.bfloat16, "cuda", seed=8)
+    lrs = [1e-4 * (k + 1) for k in range(len(shapes))]
+    opt = AdamW([{"params": [p], "lr": lr} for p, lr in zip(params, lrs)], dtype=torch.bfloat16,
+                storage_device="cuda", seed=2, **{k: v for k, v in HP.items() if k != "lr"})
+    mirrors = [Mirror([p], torch.bfloat16, 2, ids=[k], **{**HP, "lr": lr}) for k, (p, lr) in enumerate(zip(params, lrs))]
+    for s in range(3):
+        grads = make_grads(shapes, torch.bfloat16, s)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step()
+        for k, mir in enumerate(mirrors):
+            mir.apply([grads[k]])
+            check(opt, [params[k]], mir)
