@@ -140,13 +140,22 @@ class ShardPlan:
         self.verified = True
 
     # ------------------------------------------------------------------ flattening
+    def _peer_bucket(self) -> Optional[Bucket]:
+        """The one bucket of this plan that gets peer-mapped buffers: the largest in bytes.  An
+        optimizer launch carries one shared parameter region and one shared gradient region, so a
+        model with parameters of several dtypes keeps its smaller buckets on the NCCL collectives."""
+        if not self.buckets:
+            return None
+        return max(self.buckets.values(),
+                   key=lambda b: b.segment * torch.empty((), dtype=b.dtype).element_size())
+
     def _allocate_flat(self, b: Bucket) -> torch.Tensor:
         """The flat parameter buffer of a bucket.  On NCCL ranks with CUDA parameters it is
         allocated as peer-mapped ("symmetric") memory so that the optimizer kernel can store the
         owners' new values directly into every rank's copy; anything else gets plain memory and
         the all-gather path.  Set RT_ZERO_FUSED_PUSH=0 to force the all-gather path."""
         n = b.segment * self.world_size
-        want = (b.device.type == "cuda" and self.world_size > 1 and self.world_size - 1 <= 15 and
+        want = (b is self._peer_bucket() and b.device.type == "cuda" and self.world_size > 1 and self.world_size - 1 <= 15 and
                 dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl" and
                 dist.get_world_size() == self.world_size and os.environ.get("RT_ZERO_FUSED_PUSH", "1") != "0")
         if want:

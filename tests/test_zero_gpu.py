@@ -12,19 +12,24 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(257, 64), (64,), (1000, 33), (33,), (4096,), (8, 8, 8), (70001,), (5,), (129, 128)]
+SHAPES = [(257, 64), (64,), (1000, 33), (33,), (4096,), (8, 8, 8), (70001, 1), (5,), (129, 128)]
 HP = dict(lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
 STEPS = 5
 
 
 def _params(device):
+    """bf16 weights and fp32 vectors (norm scales are often kept in fp32): two flat buckets, of which
+    only the larger one is peer-mapped."""
     g = torch.Generator().manual_seed(0)
-    return [torch.nn.Parameter((torch.randn(s, generator=g) * 0.02).bfloat16().to(device)) for s in SHAPES]
+    return [torch.nn.Parameter((torch.randn(s, generator=g) * 0.02).to(torch.float32 if len(s) == 1 else torch.bfloat16)
+                               .to(device)) for s in SHAPES]
 
 
 def _grad(step, rank, k, shape, exact=True):
     g = torch.Generator().manual_seed(1000 * step + 10 * rank + k)
-    if not exact:
+    if not exact and len(shape) > 1:
+        # random values for the (bf16, peer-mapped) weights only: the fp32 vectors go through NCCL,
+        # whose summation order is unspecified beyond two ranks
         return (torch.randn(shape, generator=g) * 1e-3).bfloat16()
     # multiples of 2^-14 with few significant bits: sums of up to 8 ranks are exact in bf16, so the
     # order in which NCCL adds them cannot matter
@@ -55,7 +60,7 @@ def _worker(rank, world, port, out, mode, exact):
         for step in range(STEPS):
             # a "backward": every parameter receives this rank's gradient through autograd; on odd
             # steps in two micro-batches (gradient accumulation) whose halves add up exactly
-            grads = [_grad(step, rank, k, p.shape, exact).to(dev) for k, p in enumerate(params)]
+            grads = [_grad(step, rank, k, p.shape, exact).to(dev, p.dtype) for k, p in enumerate(params)]
             if step % 2 == 1 and exact:
                 halves = [(g * 0.5, g - g * 0.5) for g in grads]      # powers of two: exact in bf16
                 for part in (0, 1):
@@ -68,10 +73,10 @@ def _worker(rank, world, port, out, mode, exact):
                 p.grad = None if step % 2 == 0 else p.grad.zero_()
         torch.cuda.synchronize()
         from ramtorch_b200._shard_plan import plan_for
-        modes = sorted({str(b.mode) for b in plan_for(rpg).buckets.values()})
-        assert modes == (["push"] if fused else ["None"]), modes
-        pulls = {b.gpeer_ptrs is not None for b in plan_for(rpg).buckets.values()}
-        assert pulls == {mode == "peer-push+grad-pull"}
+        buckets = {str(b.dtype): b for b in plan_for(rpg).buckets.values()}
+        big, small = buckets["torch.bfloat16"], buckets["torch.float32"]
+        assert str(big.mode) == ("push" if fused else "None") and small.peer_ptrs is None and small.mode is None
+        assert (big.gpeer_ptrs is not None) == (mode == "peer-push+grad-pull") and small.gpeer_ptrs is None
         out.put((rank, "ok", [p.detach().float().cpu() for p in params]))
     except Exception as e:
         import traceback
@@ -96,7 +101,10 @@ def _single_process(world, exact=True, fp32_sum=False):
             total = _grad(step, 0, k, p.shape, exact).float()
             for r in range(1, world):
                 total = total + _grad(step, r, k, p.shape, exact).float()
-            p.grad = (total if fp32_sum else total.bfloat16()).to(dev)
+            if p.dtype == torch.float32:
+                p.grad = total.to(dev)           # fp32 bucket: NCCL sums fp32 (exact here, or two ranks)
+            else:
+                p.grad = (total if fp32_sum else total.bfloat16()).to(dev)
         opt.step()
     return [p.detach().float().cpu() for p in params]
 
