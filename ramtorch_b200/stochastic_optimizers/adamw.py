@@ -340,6 +340,10 @@ class AdamW(Optimizer):
                     if group["centralization"] != 0:
                         raise NotImplementedError("centralization != 0 needs parameter, gradient and moments "
                                                   "on the GPU (it is not available on the streamed path)")
+                    if grad.is_cuda and SP.pull_bucket_for(index, [grad.data_ptr()]) is not None:
+                        raise RuntimeError("ZeRO-2 fused gradient reduction (RT_ZERO2_FUSED_PULL=1) needs the moments in "
+                                           "HBM (storage_device on the GPU): the streamed path does not sum the ranks' "
+                                           "gradients")
                     streamed.append((index,) + entry)
 
         if len(hyper_rows) > 1024:
