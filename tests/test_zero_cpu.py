@@ -88,7 +88,8 @@ def _model(seed=0):
 
 def _worker(rank, world, port, scenario, out):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
     try:
         result = SCENARIOS[scenario](rank, world)
         out.put((rank, "ok", result))
@@ -178,12 +179,31 @@ def _scenario_ramtorch_hooks(rank, world):
     return owner_ok and bool((plain == 2.0).all()) and bool((w == 0).all())
 
 
-SCENARIOS = {"full_loop": _scenario_full_loop, "plan_mismatch": _scenario_plan_mismatch,
+def _scenario_rank_leaves(rank, world):
+    """Failure made on the host: rank 1 leaves between steps (no collective in flight).  Rank 0's
+    next redistribution must end with an exception within the process-group timeout, not hang."""
+    params = [torch.zeros(4), torch.ones(6)]
+    rpg = create_zero_param_groups([{"params": params}], world)
+    broadcast_zero_params(rpg)                   # one healthy step with everybody present
+    if rank == 1:
+        return True                              # leaves: the worker tears its process group down
+    import time
+    t0 = time.time()
+    try:
+        for _ in range(3):
+            broadcast_zero_params(rpg)
+            time.sleep(0.5)
+    except Exception as e:                        # gloo: connection closed / reset / timed out
+        return time.time() - t0 < 30 and isinstance(e, (RuntimeError, ValueError))
+    return False
+
+
+SCENARIOS = {"rank_leaves": _scenario_rank_leaves, "full_loop": _scenario_full_loop, "plan_mismatch": _scenario_plan_mismatch,
              "ramtorch_hooks": _scenario_ramtorch_hooks}
 
 
 @pytest.mark.parametrize("scenario,world", [("full_loop", 2), ("full_loop", 3), ("plan_mismatch", 2),
-                                            ("ramtorch_hooks", 2)])
+                                            ("ramtorch_hooks", 2), ("rank_leaves", 2)])
 def test_gloo_ranks(scenario, world):
     results = _spawn(scenario, world)
     assert len(results) == world
