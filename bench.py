@@ -426,9 +426,15 @@ def main():
             for bk in _pf(rpg).buckets.values():
                 bk.gflat.normal_(0, 1e-3)          # every rank holds a gradient for every parameter
 
+    rs_events = []
+
     def one_step(k):
         if grad_sync:
             reduce_gradients_now(rpgs[k % len(rpgs)])
+            if rs_events is not None and len(rs_events) < 4096:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                rs_events.append(e)
         steppers[k % len(steppers)].step()
 
     def redistribute(k):
@@ -442,6 +448,7 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(local) if rank == 0 else None
+    rs_events.clear()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     launches0 = N.stats()["kernel_launches"]
     t_wall0 = time.time()
@@ -462,6 +469,10 @@ def main():
     upd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)) / args.steps
     ag_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(args.steps)) / args.steps
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+    sync_ms = None
+    if grad_sync and len(rs_events) == args.steps:
+        # part of t_update spent in the gradient reduction (NCCL reduce-scatter, or the barrier of the fused path)
+        sync_ms = sum(ev[2 * k].elapsed_time(rs_events[k]) for k in range(args.steps)) / args.steps
     elems = torch.tensor([float(owned_elems)], device=device, dtype=torch.float64)
     if world > 1:
         t = torch.tensor([total_ms, upd_ms, ag_ms], device=device, dtype=torch.float64)
@@ -606,7 +617,8 @@ def main():
                            "parallelism": f"zero1x{world}" if world > 1 else "single"},
                 "roofline": roofline, "e2e": e2e, "cpu_baseline": base, "gpu_launches": int(launches),
                 "clocks": clocks, "t_update_ms": upd_ms, "t_all_gather_ms": ag_ms if world > 1 else 0.0,
-                "t_reduce_scatter_ms": rs_ms, "zero1_redistribution": redistribution,
+                "t_reduce_scatter_ms": rs_ms, "t_grad_sync_inside_update_ms": sync_ms,
+                "zero1_redistribution": redistribution,
                 "zero2_reduction": (None if world == 1 else
                                     "inside t_update: fused peer loads in the optimizer kernel" if args.fused_grad_pull else
                                     "inside t_update: NCCL reduce-scatter before the kernel" if grad_sync else

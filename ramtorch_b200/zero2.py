@@ -31,13 +31,13 @@ def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int) -> None:
     segments this rank does not own so that a later micro-batch accumulates onto zeros there
     (which keeps gradient accumulation equal to the reference's reduce-every-backward)."""
     bucket.ready = 0
+    written, bucket.grads_written = bucket.grads_written, False
     if plan.world_size == 1 or not dist.is_initialized():
         return
     if bucket.gpeer_ptrs is not None:
         # fused reduction: the optimizer kernel will read every rank's copy itself; all that is
         # needed here is that no rank starts reading before every rank has finished writing
-        if bucket.grads_written:
-            bucket.grads_written = False
+        if written:
             dist.all_reduce(_barrier_token(bucket))
         return
     mine = bucket.rank_segment(bucket.gflat, rank)
@@ -61,7 +61,8 @@ def finish_grad_sync() -> None:
     times, as with any collective."""
     for plan in list(_ACTIVE_PLANS):
         for bucket in plan.buckets.values():
-            if bucket.gflat is not None and (bucket.ready > 0 or bucket.grads_written):
+            if bucket.gflat is not None and (bucket.ready > 0 or
+                                             (bucket.gpeer_ptrs is not None and bucket.grads_written)):
                 _reduce_bucket(plan, bucket, plan.current_rank)
 
 
