@@ -210,3 +210,22 @@ def test_gloo_ranks(scenario, world):
     for rank, status, payload in results:
         assert status == "ok", f"rank {rank}: {payload}"
         assert payload is True, f"rank {rank} returned {payload}"
+
+
+def test_world_size_one_needs_no_process_group():
+    """The single-process case of the README loop: every call is a no-op or purely local."""
+    model = _model()
+    rpg = create_zero_param_groups([{"params": list(model.parameters())}], 1)
+    handles = setup_grad_sharding_hooks(rpg, 0)
+    assert len(handles) == len(list(model.parameters()))
+    model(torch.randn(4, 13)).square().sum().backward()
+    want = [p.grad.clone() for p in model.parameters()]
+    from ramtorch_b200.zero2 import finish_grad_sync
+    finish_grad_sync()
+    assert broadcast_zero_params(rpg) is None
+    for p, g in zip(model.parameters(), want):
+        assert torch.equal(p.grad, g)
+    # the parameters were packed into the flat buffer without changing their values
+    fresh = _model()
+    for p, q in zip(model.parameters(), fresh.parameters()):
+        assert torch.equal(p, q)
