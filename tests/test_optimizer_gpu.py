@@ -359,3 +359,29 @@ def test_more_hyper_rows_than_ride_along_with_a_launch():
         for k, mir in enumerate(mirrors):
             mir.apply([grads[k]])
             check(opt, [params[k]], mir)
+
+
+def test_large_all_bf16_tensor_takes_the_long_cta_path_bit_exactly():
+    """2^29 + 8200 elements with bf16 moments: the plan gives this tensor CTAs of four 8192-element
+    pieces; slices recomputed by the checker at their own index0 must match bit for bit."""
+    from ramtorch_b200 import AdamW
+    dev = torch.device("cuda")
+    n = (1 << 29) + 8200
+    gen = torch.Generator(device=dev).manual_seed(1)
+    p = (torch.randn(n, device=dev, generator=gen) * 0.02).bfloat16()
+    p.grad = (torch.randn(n, device=dev, generator=gen) * 1e-3).bfloat16()
+    opt = AdamW([p], dtype=torch.bfloat16, storage_device=dev, seed=13, **HP)
+    st = opt.state[p]
+    st["ema"].copy_(torch.randn(n, device=dev, generator=gen) * 1e-3)
+    st["ema_squared"].copy_((torch.randn(n, device=dev, generator=gen) * 1e-6).abs())
+    st["step"] = 41
+    p0, m0, v0 = p.clone(), st["ema"].clone(), st["ema_squared"].clone()
+    opt.step()
+    h = oracle.make_hyper(HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"], 42, shared_draws=True)
+    for lo in (0, 8 * 4097, 32768 * 1000 + 8192, n // 2 + 24, n - 65536):
+        sl = slice(lo, min(n, lo + 65536))
+        ps, gs, ms, vs = (to_numpy(t[sl]) for t in (p0, p.grad, m0, v0))
+        oracle.adamw_sr(ps, gs, ms, vs, oracle.BF16, oracle.BF16, oracle.BF16, h, seed=13, tensor_id=0, index0=lo)
+        assert bits_equal(ps, to_numpy(p[sl])) == 0
+        assert bits_equal(ms, to_numpy(st["ema"][sl])) == 0
+        assert bits_equal(vs, to_numpy(st["ema_squared"][sl])) == 0
