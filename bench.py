@@ -500,7 +500,8 @@ def main():
             # the other ranks' buffers, so its target time is the slower of the HBM time and the
             # NVLink time (bytes leaving this GPU / measured peer-copy rate per direction)
             nvlink_peak = 770.0
-            egress = 2.0 * per_rank * (world - 1)
+            # parameters pushed to the peers, plus (fused reduction) this rank's gradients read by the peers
+            egress = 2.0 * per_rank * (world - 1) * (2 if args.fused_grad_pull else 1)
             t_hbm = bytes_per_elem * per_rank / (peak * 1e9)
             t_link = egress / (nvlink_peak * 1e9)
             target = max(t_hbm, t_link)
