@@ -158,3 +158,28 @@ def stats() -> dict:
 
 def stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+# ------------------------------------------------------------------ tracing
+NVTX = os.environ.get("RT_NVTX", "0") == "1"
+
+
+class _Range:
+    """NVTX range around a phase of the step (RT_NVTX=1); free when tracing is off."""
+
+    __slots__ = ("name",)
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
+
+
+def trace(name: str) -> _Range:
+    return _Range(name)

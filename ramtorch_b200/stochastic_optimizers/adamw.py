@@ -355,7 +355,7 @@ class AdamW(Optimizer):
 
         for index, entries in resident.items():
             used.add(index)
-            with torch.cuda.device(index):
+            with N.trace("rt.step.resident"), torch.cuda.device(index):
                 stream = N.stream_ptr(index)
                 row_info = self._row_means(lib, index, entries, centered.get(index, {}), stream)
                 plan = self._plan_for(index, entries, row_info)
@@ -387,7 +387,7 @@ class AdamW(Optimizer):
             jobs.append((index, pd, grad, ema, ema_sq, tid, hi, codes, chunk))
         for index, pd, grad, ema, ema_sq, tid, hi, codes, chunk in jobs:
             used.add(index)
-            with torch.cuda.device(index):
+            with N.trace("rt.step.streamed"), torch.cuda.device(index):
                 staging = self._staging_for(index, ring_bytes[index])
                 cfg = N.OffloadCfg(chunk, self.offload_ring_depth, 1, staging.data_ptr(), staging.numel())
                 N.check(lib.rt_adamw_sr_offload(pd.data_ptr(), grad.data_ptr(), ema.data_ptr(),

@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ._native import trace as _trace
 from ._shard_plan import ShardPlan, plan_for
 
 PARAM_IDS_KEY = "rt_param_ids"
@@ -72,7 +73,7 @@ def broadcast_zero_params(rank_param_groups, async_op=True):
         return
     rank = dist.get_rank()
     works = []
-    with torch.no_grad():
+    with _trace("rt.zero1.redistribute"), torch.no_grad():
         barrier_needed = False
         for bucket in plan.buckets.values():
             if _owners_pushed(plan, bucket, rank):

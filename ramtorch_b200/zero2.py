@@ -20,6 +20,7 @@ import weakref
 import torch
 import torch.distributed as dist
 
+from ._native import trace as _trace
 from ._shard_plan import Bucket, ShardPlan, plan_for
 from .helpers import ZERO2_HOOK_NAME, register_ramtorch_hook
 
@@ -40,12 +41,13 @@ def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int) -> None:
         if written:
             dist.all_reduce(_barrier_token(bucket))
         return
-    mine = bucket.rank_segment(bucket.gflat, rank)
-    work = dist.reduce_scatter_tensor(mine, bucket.gflat, op=dist.ReduceOp.SUM, async_op=True)
-    work.wait()   # orders the current stream after the collective; the host does not block on NCCL
-    lo, hi = rank * bucket.segment, (rank + 1) * bucket.segment
-    bucket.gflat[:lo].zero_()
-    bucket.gflat[hi:].zero_()
+    with _trace("rt.zero2.reduce_scatter"):
+        mine = bucket.rank_segment(bucket.gflat, rank)
+        work = dist.reduce_scatter_tensor(mine, bucket.gflat, op=dist.ReduceOp.SUM, async_op=True)
+        work.wait()   # orders the current stream after the collective; the host does not block on NCCL
+        lo, hi = rank * bucket.segment, (rank + 1) * bucket.segment
+        bucket.gflat[:lo].zero_()
+        bucket.gflat[hi:].zero_()
 
 
 def _barrier_token(bucket: Bucket) -> torch.Tensor:
