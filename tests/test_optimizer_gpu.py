@@ -385,3 +385,28 @@ def test_large_all_bf16_tensor_takes_the_long_cta_path_bit_exactly():
         assert bits_equal(ps, to_numpy(p[sl])) == 0
         assert bits_equal(ms, to_numpy(st["ema"][sl])) == 0
         assert bits_equal(vs, to_numpy(st["ema_squared"][sl])) == 0
+
+
+def test_streamed_call_rejects_a_short_staging_buffer_before_copying_anything():
+    """Host-side fault injection: a staging ring that is too small for the requested chunk is an
+    argument error (nothing copied, nothing launched, tensors untouched)."""
+    import ctypes
+    from ramtorch_b200 import _native as N
+    lib = N.lib()
+    n = 100000
+    p = torch.zeros(n, dtype=torch.bfloat16).pin_memory()
+    g = torch.ones(n, dtype=torch.bfloat16).pin_memory()
+    m = torch.zeros(n, dtype=torch.bfloat16).pin_memory()
+    v = torch.zeros(n, dtype=torch.bfloat16).pin_memory()
+    need = lib.rt_offload_staging_bytes(32768, 3, 0, 0, 0, 1, 1, 1, 1)
+    staging = torch.empty(need // 2, dtype=torch.uint8, device="cuda")
+    cfg = N.OffloadCfg(32768, 3, 0, staging.data_ptr(), staging.numel())
+    h = N.make_hyper(1e-3, (0.9, 0.999), 1e-8, 0.0, 1)
+    before = N.stats()
+    rc = lib.rt_adamw_sr_offload(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), n, 0, 0, 0,
+                                 ctypes.byref(h), 0, 0, ctypes.byref(cfg), N.stream_ptr(torch.device("cuda", 0)))
+    assert rc == -6 and b"staging buffer too small" in lib.rt_last_error()
+    after = N.stats()
+    assert after == before
+    torch.cuda.synchronize()
+    assert float(p.float().abs().sum()) == 0 and float(m.float().abs().sum()) == 0
