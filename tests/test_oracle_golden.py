@@ -128,3 +128,50 @@ def test_zero1_golden_is_round_robin_per_group():
             for j in range(n):
                 assert k in c["ownership"][str(j % w)][gi]
                 k += 1
+
+
+def test_shared_draws_layout_is_the_rotated_block_of_stream_zero():
+    """RT_HYPER_SHARED_DRAWS in the checker: element i of stream s takes draw ((i & 7) + 2 s) & 7 of
+    the stream-0 block of its group -- restated here with the numpy Philox."""
+    n, seed, tid, step, index0 = 1000, 77, 3, 9, 16
+    h = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, step, shared_draws=True)
+    rng = np.random.default_rng(0)
+    p = oracle.f32_to_bf16_bits_rn(rng.normal(0, 0.02, n).astype(np.float32))
+    g = oracle.f32_to_bf16_bits_rn(rng.normal(0, 1e-3, n).astype(np.float32))
+    m = oracle.f32_to_bf16_bits_rn(rng.normal(0, 1e-3, n).astype(np.float32))
+    v = oracle.f32_to_bf16_bits_rn(np.abs(rng.normal(0, 1e-6, n)).astype(np.float32))
+    p1, m1, v1 = p.copy(), m.copy(), v.copy()
+    fp, fm, fv = oracle.adamw_sr(p1, g, m1, v1, oracle.BF16, oracle.BF16, oracle.BF16, h, seed=seed,
+                                 tensor_id=tid, index0=index0, want_f32=True)
+    i = np.arange(index0, index0 + n)
+    block = oracle.draws_np(seed, tid, step, 0, (index0 // 8) * 8, ((index0 + n + 7) // 8) * 8 - (index0 // 8) * 8)
+    base = (index0 // 8) * 8
+    for s, (f32, out) in enumerate(((fp, p1), (fm, m1), (fv, v1))):
+        lane = (i & ~7) | (((i & 7) + 2 * s) & 7)
+        r = block[lane - base]
+        assert (oracle.sr_round_np(f32, r) == out).all()
+
+
+def test_bench_workload_generators_match_the_configs():
+    import bench
+    shapes = bench.llama_shapes()
+    assert len(shapes) == 291
+    assert sum(int(np.prod(s)) for s in shapes) == 6_738_415_616
+    ragged = bench.ragged_shapes()
+    assert len(ragged) == 20000
+    total = sum(int(np.prod(s)) for s in ragged)
+    assert 7.4e9 < total < 7.6e9                      # log-uniform(64, 4194304) x 20000, as specified
+    assert all(len(s) == 1 for s in ragged if np.prod(s) < 16384)
+
+
+def test_alias_package_serves_the_reference_import_paths():
+    import ramtorch
+    import ramtorch_b200
+    from ramtorch.stochastic_optimizers.adamw import AdamW, copy_stochastic_
+    from ramtorch.zero1 import broadcast_zero_params, create_zero_param_groups
+    from ramtorch.zero2 import setup_grad_sharding_hooks
+    assert AdamW is ramtorch_b200.AdamW and ramtorch.AdamW is AdamW
+    assert create_zero_param_groups is ramtorch_b200.zero1.create_zero_param_groups
+    assert setup_grad_sharding_hooks is ramtorch_b200.zero2.setup_grad_sharding_hooks
+    with pytest.raises(AttributeError):
+        ramtorch.Linear
