@@ -26,6 +26,11 @@ import torch.distributed as dist
 
 ALIGN_BYTES = 256
 
+# The fused paths use plain peer loads and stores only; keep PyTorch's symmetric memory from also
+# binding the buffers to an NVLink multicast object (nothing here uses multimem, and a rank that
+# dies while bound to one can disturb its peers' links).  Respect an explicit user setting.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
 
 class Bucket:
     """All flattened parameters of one (device, dtype)."""
