@@ -265,15 +265,17 @@ int rt_adamw_sr_multi_static(const rt_tensor_desc* tensors, int64_t count,
  * Host-offloaded step (adamw.py:152-170, 204-222 when parameters and/or state live in CPU
  * RAM): streams one tensor through the GPU in chunks.  Each of p, g, m, v may be a host
  * pointer or a device pointer (pinned host memory overlaps its copies with the kernel;
- * pageable host memory works but every copy is then synchronous); host-resident ones are
- * staged through the ring of
- * device buffers in `staging` (at least ring_depth * chunk_elems * bytes-per-element of
- * the host-resident tensors).  H2D, kernel and D2H run on three library-owned side
- * streams, ordered by events; `cuda_stream` is made to wait for the pipeline's completion
- * and the pipeline waits for work already enqueued on `cuda_stream`.
+ * pageable host memory works but every copy is then synchronous).  Host-resident ones are
+ * staged through the ring of device buffers in `staging`, which must hold at least
+ * rt_offload_staging_bytes(...) for this tensor; the slots are staging_bytes / ring_depth
+ * each, so one larger buffer serves tensors of any size, dtype and residency without
+ * draining the pipeline between them.  H2D, kernel and D2H run on three library-owned side
+ * streams, ordered by events; the pipeline waits for work already enqueued on
+ * `cuda_stream`, and `cuda_stream` is made to wait for the pipeline's completion (at the end
+ * of the call, or in rt_offload_join when defer_join is set).
  */
 typedef struct rt_offload_cfg {
-  int64_t chunk_elems;  /* multiple of 8; 0 = default (128 Mi elements / 8) */
+  int64_t chunk_elems;  /* multiple of 8; 0 = default (2^24 elements) */
   int ring_depth;       /* 2..8; 0 = default 3 */
   int defer_join;       /* 0: cuda_stream waits for this call's work before the call returns;
                            1: it does not -- call rt_offload_join once after the last tensor, so
