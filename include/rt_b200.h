@@ -123,7 +123,7 @@ typedef struct rt_debug {
 } rt_debug;
 
 /*
- * a1 — stochastic rounding alone: replaces copy_stochastic_(target, source, seed)
+ * Stochastic rounding alone: replaces copy_stochastic_(target, source, seed)
  * (adamw.py:6-30).  source: n fp32 on the device; target: n bf16 on the device.
  * rand16 != NULL injects the draws, otherwise Philox (seed, tensor_id, step, stream).
  */
@@ -132,7 +132,7 @@ int rt_sr_round_bf16(void* target_bf16, const float* source_f32, int64_t n,
                      uint32_t step, uint32_t stream_id, void* cuda_stream);
 
 /*
- * a3-a6 — one fused step over ONE contiguous tensor resident in device memory: replaces the
+ * One fused step over ONE contiguous tensor resident in device memory: replaces the
  * body of AdamW.step for one parameter (adamw.py:160-222).  p, m, v are updated in place.
  * index0 is the tensor-local index of element 0 of the pointers given (non-zero when the
  * caller passes a slice of a larger tensor, e.g. a streamed chunk or a ZeRO shard); it must
@@ -145,7 +145,7 @@ int rt_adamw_sr_flat(void* p, const void* g, void* m, void* v, int64_t n,
                      const rt_debug* debug, void* cuda_stream);
 
 /*
- * a8 -- gradient centralization (adamw.py:179-184): out[r] = mean over row r of g, fp32, for a
+ * Gradient centralization (adamw.py:179-184): out[r] = mean over row r of g, fp32, for a
  * gradient viewed as rows x row_len (rows = size of dim 0, or 1 for tensors with fewer than two
  * dimensions, which the reference reduces as a whole).  The fused kernels subtract
  * centralization * out[(index0 + i) / row_len] from g[i] when a tensor carries row_mean and its
