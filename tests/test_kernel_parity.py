@@ -110,7 +110,7 @@ def test_index0_offsets_select_the_same_draws_as_the_whole_tensor():
 def test_debug_kernel_taps_and_injected_draws(kinds):
     n = 30001
     got, want, f32_want, taps = run_both(n, *kinds, inject=True, taps=True)
-    # fp32 pre-rounding update: north-star tolerance 1e-6 relative; in fact identical bits
+    # fp32 pre-rounding update: the required tolerance is 1e-6 relative; in fact the bits are identical
     for a, b in zip(taps, f32_want):
         assert bits_equal(a, b) == 0
     # identical random bits -> bit-exact results
