@@ -242,6 +242,8 @@ WORKLOADS = {
     "c1": "config 1: 16,777,216-element bf16 parameter, bf16 moments, t=11, rotating over 12 buffer sets",
     "c3": "config 3: Llama-style 32-layer decoder shapes (291 tensors, 6.74e9 elements), bf16 moments, ZeRO-1",
     "c5": "config 5: 20,000 ragged bf16 tensors, sizes log-uniform in [64, 4194304], bf16 moments, ZeRO-1",
+    "list": "a list of --list-count equal bf16 tensors of --elems elements each, bf16 moments (for profiling the "
+            "multi-tensor path on a small case)",
     "c4": "config 4: 8e9 bf16 parameters + bf16 moments in pinned host RAM (60 tensors of 2^27 elements, split "
           "over the ranks), gradients in pinned host RAM too (where the reference's Linear leaves them), streamed "
           "in 256 MiB chunks per tensor through a 2-slot ring",
@@ -336,6 +338,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--elems", type=int, default=ELEMS_PER_GPU, help="elements per GPU for c2/bf16 (default 2^30)")
+    ap.add_argument("--list-count", type=int, default=64, help="number of tensors of the 'list' workload")
     ap.add_argument("--e2e-steps", type=int, default=4)
     ap.add_argument("--fast-math", action="store_true", help="approximate sqrt/reciprocal in p' (off by default)")
     ap.add_argument("--independent-draws", action="store_true",
@@ -407,6 +410,8 @@ def main():
         owned_elems = [make_set([(1 << 24,)] * world, k) for k in range(12)][0]
     elif wl == "c3":
         owned_elems = make_set(llama_shapes(), 0)
+    elif wl == "list":
+        owned_elems = make_set([(args.elems,)] * args.list_count, 0)
     else:
         owned_elems = make_set(ragged_shapes(), 0)
     torch.cuda.synchronize()
