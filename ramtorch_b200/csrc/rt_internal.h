@@ -85,6 +85,7 @@ int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* ch
                  const rt_hyper* hypers, const DevTensor& one, const rt_hyper& one_h,
                  uint64_t seed, int64_t nblocks, cudaStream_t stream, uint32_t flags,
                  const PeerTables* peers, const HyperPack* pack);
+int check_launchable(int pd, int gd, int sd, uint32_t flags, const PeerTables* peers);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
 int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,

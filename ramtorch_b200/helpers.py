@@ -3,15 +3,18 @@
 Only the two-attribute protocol of the reference (ramtorch/helpers.py:8-50) that
 ``zero2.setup_grad_sharding_hooks`` relies on and that the reference's ``Linear`` backward consumes
 (ramtorch/modules/linear.py:76-94): a tensor carries ``<name>`` (an ``OrderedDict`` id -> callable)
-and ``<name>_counter`` (next id).  The model-surgery helpers of that file are not part of this
-package.
+and ``<name>_counter`` (next id).  Of the model-surgery helpers of that file only
+``reattach_is_ramtorch_flags`` (helpers.py:229-253) is provided: ZeRO-1/2 here branch on the
+per-tensor ``is_ramtorch`` flag, which a deserialised model has lost.
 """
 from __future__ import annotations
 
 from collections import OrderedDict
+from itertools import chain
 from typing import Callable
 
 import torch
+from torch import nn
 
 ZERO2_HOOK_NAME = "_ramtorch_zero_2_hooks"
 
@@ -49,3 +52,23 @@ def invoke_ramtorch_hooks(tensor: torch.Tensor, grad: torch.Tensor, hook_name: s
         if out is not None:
             grad = out
     return grad
+
+
+def reattach_is_ramtorch_flags(module: nn.Module) -> nn.Module:
+    """Put ``is_ramtorch = True`` back on the parameters and buffers that directly belong to any
+    sub-module (``module`` itself included) which declares ``is_ramtorch = True``
+    (helpers.py:229-253).
+
+    Tensor attributes do not survive ``torch.save`` / ``torch.load`` or ``copy.deepcopy``; the
+    module attribute does (``Linear`` sets it as a class-level flag, linear.py).  Call this after
+    rebuilding a model and BEFORE ``create_zero_param_groups`` / ``setup_grad_sharding_hooks``:
+    both treat a parameter without the flag as an ordinary HBM tensor (flat buffer + collective)
+    instead of CPU storage shared by all workers (zero1.py:81, zero2.py:67-72).  Returns
+    ``module``."""
+    for sub in module.modules():
+        if not getattr(sub, "is_ramtorch", False):
+            continue
+        for tensor in chain(sub.parameters(recurse=False), sub.buffers(recurse=False)):
+            if isinstance(tensor, torch.Tensor):
+                tensor.is_ramtorch = True
+    return module

@@ -25,6 +25,7 @@ from __future__ import annotations
 import ctypes
 import operator
 import warnings
+from collections import defaultdict
 from itertools import chain
 
 import numpy as np
@@ -42,6 +43,7 @@ import contextlib
 from .. import zero2 as _zero2
 
 _NULL_CTX = contextlib.nullcontext()
+_GET_EMA, _GET_EMA_SQ, _GET_STEP = (operator.itemgetter(k) for k in ("ema", "ema_squared", "step"))
 _PARAM_IDS_KEY = "rt_param_ids"
 DEVICE_GRAD_ATTR = "rt_device_grad"
 
@@ -75,6 +77,61 @@ def copy_stochastic_(target: torch.Tensor, source: torch.Tensor, seed=0):
             tmp = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
             sr_round_bf16_(tmp, src, seed=int(seed))
             target.copy_(tmp)
+
+
+class _TrackedState(defaultdict):
+    """``Optimizer.state`` that counts structural changes (an entry added, replaced or removed), so
+    that the repeat-step fast path can tell in O(1) that the per-parameter state dicts it cached
+    are still the ones in use."""
+
+    epoch = 0
+
+    def _bump(self):
+        self.epoch += 1
+
+    def __setitem__(self, key, value):
+        self.epoch += 1
+        super().__setitem__(key, value)
+
+    def __delitem__(self, key):
+        self.epoch += 1
+        super().__delitem__(key)
+
+    def pop(self, *a):
+        self.epoch += 1
+        return super().pop(*a)
+
+    def popitem(self):
+        self.epoch += 1
+        return super().popitem()
+
+    def clear(self):
+        self.epoch += 1
+        super().clear()
+
+    def update(self, *a, **k):
+        self.epoch += 1
+        super().update(*a, **k)
+
+    def setdefault(self, key, default=None):
+        self.epoch += 1
+        return super().setdefault(key, default)
+
+    def __reduce__(self):   # pickles like the defaultdict it stands in for
+        return (defaultdict, (dict,), None, None, iter(self.items()))
+
+
+def _fast_dispatch_ok() -> bool:
+    """Whether this torch build exposes what ``AdamW.step`` reads to decide that the stock
+    ``Optimizer.step`` wrapper (profiler range + hook dispatch) has nothing to do.  If any name is
+    missing, every step goes through the stock wrapper."""
+    return (hasattr(_torch_opt, "_global_optimizer_pre_hooks") and
+            hasattr(_torch_opt, "_global_optimizer_post_hooks") and
+            hasattr(torch.autograd.profiler, "_is_profiler_enabled") and
+            hasattr(Optimizer, "profile_hook_step") and hasattr(Optimizer, "_patch_step_function"))
+
+
+_FAST_DISPATCH = _fast_dispatch_ok()
 
 
 class _DevicePlan:
@@ -173,6 +230,7 @@ class AdamW(Optimizer):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                         centralization=centralization)
         super().__init__(params, defaults)
+        self._track_state()
 
         self.chunk_size = chunk_size
         self.optim_state_dtype = dtype
@@ -198,6 +256,23 @@ class AdamW(Optimizer):
         self._allocate_states(fresh)
 
     # ------------------------------------------------------------------ bookkeeping
+    def _track_state(self):
+        if not isinstance(self.state, _TrackedState):
+            tracked = _TrackedState(dict)
+            tracked.update(self.state)
+            self.state = tracked
+        self.state._bump()
+
+    def __setstate__(self, state):
+        # load_state_dict() and unpickling replace self.state and the group dicts wholesale: whatever
+        # the repeat-step fast path and the device plans remembered is stale from here on
+        super().__setstate__(state)
+        self._track_state()
+        self._fast = None
+        for plan in getattr(self, "_plans", {}).values():
+            plan.close()
+        self._plans = {}
+
     def add_param_group(self, param_group):
         super().add_param_group(param_group)
         group = self.param_groups[-1]
@@ -244,19 +319,24 @@ class AdamW(Optimizer):
         return buf
 
     # ------------------------------------------------------------------ the step
-    def _patch_step_function(self) -> None:
-        # torch wraps every Optimizer.step in a profiler range plus hook dispatch (~35 us per call,
-        # as much as the fused kernel needs for 16M elements).  step() below keeps the same
-        # behaviour -- pre/post hooks run, the range is opened while a profiler is recording --
-        # but skips the machinery when there is nothing to run or record.
-        self._zero_grad_profile_name = f"Optimizer.zero_grad#{self.__class__.__name__}.zero_grad"
+    if _FAST_DISPATCH:
+        def _patch_step_function(self) -> None:
+            # torch wraps every Optimizer.step in a profiler range plus hook dispatch (~35 us per
+            # call, as much as the fused kernel needs for 16M elements).  step() below keeps the
+            # same behaviour -- pre/post hooks run, the range is opened while a profiler is
+            # recording -- but skips the machinery when there is nothing to run or record.
+            self._zero_grad_profile_name = f"Optimizer.zero_grad#{self.__class__.__name__}.zero_grad"
 
-    def step(self, closure=None):
-        if (self._optimizer_step_pre_hooks or self._optimizer_step_post_hooks or
-                _torch_opt._global_optimizer_pre_hooks or _torch_opt._global_optimizer_post_hooks or
-                getattr(torch.autograd.profiler, "_is_profiler_enabled", True)):
-            return _HOOKED_STEP(self, closure)
-        return self._step(closure)
+        def step(self, closure=None):
+            if (self._optimizer_step_pre_hooks or self._optimizer_step_post_hooks or
+                    _torch_opt._global_optimizer_pre_hooks or _torch_opt._global_optimizer_post_hooks or
+                    torch.autograd.profiler._is_profiler_enabled):
+                return _HOOKED_STEP(self, closure)
+            return self._step(closure)
+    else:  # pragma: no cover - a torch build without the names inspected above
+        def step(self, closure=None):
+            # the base class wraps this method with its own profiler range and hook dispatch
+            return self._step(closure)
 
     def _step(self, closure=None):
         loss = None
@@ -278,6 +358,7 @@ class AdamW(Optimizer):
         centered = {}   # device index -> {position in resident[index]: number of rows}
         skipped_empty = False
         late = []
+        stepped = []    # state dicts whose counter advances with this step
         for gi, group in enumerate(self.param_groups):
             for p in group["params"]:
                 grad = _grad_of(p)
@@ -295,13 +376,14 @@ class AdamW(Optimizer):
                 if grad is None:
                     continue
                 state = self.state[p]
-                state["step"] += 1
-                key = (gi, state["step"])
+                t = state["step"] + 1     # written back once every tensor of the step has been validated
+                stepped.append(state)
+                key = (gi, t)
                 hi = hyper_index.get(key)
                 if hi is None:
                     hi = hyper_index[key] = len(hyper_rows)
                     hyper_rows.append(N.make_hyper(group["lr"], group["betas"], group["eps"],
-                                                   group["weight_decay"], state["step"],
+                                                   group["weight_decay"], t,
                                                    group["centralization"], self.fast_math, self.shared_draws))
                 ema, ema_sq = state["ema"], state["ema_squared"]
                 pd = p.data
@@ -348,6 +430,8 @@ class AdamW(Optimizer):
 
         if len(hyper_rows) > 1024:
             raise ValueError("more than 1024 distinct (group, step) pairs in one step")
+        for state in stepped:     # nothing above raised: the step happens (adamw.py:177)
+            state["step"] += 1
         hyper_arr = (N.Hyper * max(len(hyper_rows), 1))(*hyper_rows)
         seed = self.seed & (2 ** 64 - 1)
         used = set()
@@ -453,7 +537,8 @@ class AdamW(Optimizer):
             p_ptrs=list(map(torch.Tensor.data_ptr, with_grad)),
             g_dtypes=[p.grad.dtype for p in with_grad],
             classes=[key for key, _ in classes], n_groups=len(self.param_groups),
-            zero_buffers=self._zero_buffer_count(index))
+            zero_buffers=self._zero_buffer_count(index),
+            state_epoch=self.state.epoch, steps=[st["step"] for st in states])
 
     @staticmethod
     def _zero_buffer_count(index):
@@ -464,6 +549,8 @@ class AdamW(Optimizer):
         groups = self.param_groups
         if len(groups) != f["n_groups"] or f["zero_buffers"] != self._zero_buffer_count(f["index"]):
             return False
+        if getattr(self.state, "epoch", None) != f["state_epoch"]:
+            return False    # a state dict was added, replaced or removed since the cache was armed
         all_params = list(chain.from_iterable(g["params"] for g in groups))
         if list(map(id, all_params)) != f["all_ids"]:
             return False
@@ -478,24 +565,24 @@ class AdamW(Optimizer):
             return False
         if any(g.is_sparse for g in grads):
             return False
-        if not (all(map(operator.is_, (st["ema"] for st in states), f["emas"])) and
-                all(map(operator.is_, (st["ema_squared"] for st in states), f["ema_sqs"]))):
+        if not (all(map(operator.is_, map(_GET_EMA, states), f["emas"])) and
+                all(map(operator.is_, map(_GET_EMA_SQ, states), f["ema_sqs"]))):
             return False
+        steps = list(map(_GET_STEP, states))
+        if steps != f["steps"]:
+            return False    # a counter was edited in place: rebuild the hyper-parameter classes
         plan = self._plans.get(f["index"])
         if plan is None or len(plan.grad_ptrs) != len(params):
             return False
         for g in groups:
             if g["centralization"] != 0:
                 return False
-        # nothing structural changed: advance the counters and launch
-        for st in states:
-            st["step"] += 1
+        # nothing structural changed: launch, then advance the counters
         rows = []
         for gi, step in f["classes"]:
             g = groups[gi]
             rows.append(N.make_hyper(g["lr"], g["betas"], g["eps"], g["weight_decay"], step + 1,
                                      g["centralization"], self.fast_math, self.shared_draws))
-        f["classes"] = [(gi, step + 1) for gi, step in f["classes"]]
         hyper_arr = (N.Hyper * len(rows))(*rows)
         gptrs = np.fromiter(map(torch.Tensor.data_ptr, grads), dtype=np.uint64, count=len(grads))
         index = f["index"]
@@ -505,6 +592,10 @@ class AdamW(Optimizer):
                     "rt_plan_set_grads")
             N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(rows), self.seed & (2 ** 64 - 1), stream),
                     "rt_adamw_sr_multi")
+        f["classes"] = [(gi, step + 1) for gi, step in f["classes"]]
+        f["steps"] = steps = [t + 1 for t in steps]
+        for st, t in zip(states, steps):
+            st["step"] = t
         for bucket in self._push_marks:
             bucket.pushed = True
         self.last_step_info = dict(launches=plan.launches, resident=len(params), streamed=0, fast=True)
@@ -562,5 +653,7 @@ class AdamW(Optimizer):
         return plan
 
 
-# the full torch behaviour (profiler range + hook dispatch) around AdamW._step, built once
-_HOOKED_STEP = Optimizer.profile_hook_step(AdamW._step)
+# The full torch behaviour (profiler range + hook dispatch) around AdamW._step, built once; only
+# used by the shortcut in AdamW.step, which exists only when this torch build has every name it
+# inspects (otherwise the base class wraps step() itself).
+_HOOKED_STEP = Optimizer.profile_hook_step(AdamW._step) if _FAST_DISPATCH else None

