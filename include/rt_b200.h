@@ -17,10 +17,19 @@
  *   g, m, v, p are widened to fp32.  With the scalars of rt_hyper:
  *     m' = fma(one_minus_beta1, g, m * beta1)                    adamw.py:190
  *     v' = fma(one_minus_beta2 * g, g, v * beta2)                adamw.py:191
- *     den = sqrt(v') / bias_correction2_sqrt + eps               adamw.py:193-195
- *     p' = (apply_decay ? p * decay : p) + (neg_step_size * m') / den   adamw.py:197-200
- *   every operation rounded to nearest-even fp32 separately except the two fma's
- *   (rt_hyper.flags & RT_HYPER_FAST_MATH relaxes den and the quotient, see below).
+ *     pw = apply_decay ? p * decay : p                           adamw.py:197-198
+ *   and then, by default,
+ *     den = fma(sqrt(v'), inv_bias_correction2_sqrt, eps)        adamw.py:193-195
+ *     p'  = fma(neg_step_size * m', 1 / den, pw)                 adamw.py:199-200
+ *   or, with rt_hyper.flags & RT_HYPER_REFERENCE_ORDER, in the reference's own operation order
+ *     den = sqrt(v') / bias_correction2_sqrt + eps
+ *     p'  = pw + (neg_step_size * m') / den
+ *   Every operation (*, /, +, sqrt, 1/x, fma) is a single correctly rounded IEEE-754 binary32
+ *   operation, so both forms are reproducible bit for bit on a CPU (sqrtf, fmaf, 1.0f / x).
+ *   m' and v' do not depend on the flag.  The default form replaces a division by a multiply-add
+ *   and the other by a reciprocal; it stays within 1e-6 of the reference order relative to
+ *   max(|p|, |p' - p|) (4e-7 worst case observed), which is the reproducibility the reference itself has
+ *   across ATen CPU builds, and it is what lets the all-bf16 kernel run at HBM speed.
  *   Write-back (adamw.py:204-222): a bf16 destination is stochastically rounded,
  *     out16 = ((bits(x) + r16) & 0xFFFF0000) >> 16                adamw.py:6-30
  *   an fp32 destination is copied, an fp16 destination is rounded to nearest-even.
@@ -78,18 +87,13 @@ typedef struct rt_hyper {
   uint32_t apply_decay;         /* weight_decay != 0 (adamw.py:197) */
   uint32_t step;                /* t; also the Philox counter word 2 */
   uint32_t flags;               /* RT_HYPER_* bits; every row of one call must agree */
-  float inv_bias_correction2_sqrt; /* f32(1 / bias_correction2_sqrt); used by RT_HYPER_FAST_MATH */
+  float inv_bias_correction2_sqrt; /* f32(1 / bias_correction2_sqrt), the division in double */
   uint32_t reserved[3];
 } rt_hyper;
 
-/* rt_hyper.flags */
-/* Approximate denominator and quotient: den = fma(sqrt.approx(v'), inv_bias_correction2_sqrt, eps),
- * p' = pw + (neg_step_size * m') * rcp.approx(den).  m' and v' are unchanged (bit-exact); p' stays
- * within 1e-6 relative of the exact contract (measured worst case in tests) but is no longer
- * bit-identical to the CPU checker.  Off by default.  Cuts ~25 instructions per element, which
- * matters for the all-bf16 variant (three Philox calls per eight elements) that is otherwise
- * bound by instruction issue rather than HBM. */
-#define RT_HYPER_FAST_MATH 1u
+/* rt_hyper.flags; bits not listed here are rejected with RT_E_CONFIG */
+/* Bit 0 is retired (it selected approximate square root and reciprocal while the exact update
+ * was bound by instruction issue; the exact default now runs at HBM speed). */
 /* One Philox block per eight elements instead of three: the block of stream 0 also serves
  * the moments, read two lanes further per stream -- element i of stream s takes draw
  * ((i & 7) + 2*s) & 7 of the block of its group.  Each rounding still sees a uniform 16-bit
@@ -99,6 +103,11 @@ typedef struct rt_hyper {
  * checker run with the same flag.  Only matters when the moments are bf16.  (The Python AdamW
  * sets it unless told otherwise; at this ABI nothing is set by default.) */
 #define RT_HYPER_SHARED_DRAWS 2u
+/* den and p' in the reference's operation order (see "Arithmetic contract"): one IEEE square
+ * root and two IEEE divisions per element.  Bit-identical to the reference's vectorised CPU step
+ * in all but ~1e-4 of the elements (where ATen's sqrt is itself not correctly rounded); about a
+ * quarter slower than the default when every operand is bf16. */
+#define RT_HYPER_REFERENCE_ORDER 4u
 
 /* Fill an rt_hyper from the constructor-level values, in double precision, as
  * adamw.py:173-188 does.  Pure host arithmetic. */
@@ -143,6 +152,20 @@ int rt_adamw_sr_flat(void* p, const void* g, void* m, void* v, int64_t n,
                      const rt_hyper* hyper, uint64_t seed, uint32_t tensor_id,
                      int64_t index0, const float* row_mean, int64_t row_len,
                      const rt_debug* debug, void* cuda_stream);
+
+/*
+ * Self-test of the kernels' square root and reciprocal.  No counterpart in the reference.
+ * The default contract needs sqrt(v') and 1/den correctly rounded; the kernels build both for
+ * two elements at a time from the hardware approximations and packed fused multiply-adds, and
+ * fall back to the CUDA built-ins outside the range where that is exact.  This entry point
+ * compares the pair routines with __fsqrt_rn / __frcp_rn on every one of the 2^32 binary32 bit
+ * patterns (~10 ms) and writes four uint64 counters to counts_dev (device memory):
+ *   [0] square-root mismatches for inputs in the fast range [2^-100, 2^100)      must be 0
+ *   [1] reciprocal mismatches for inputs in [2^-90, 2^91] (every den the fast path can form)  must be 0
+ *   [2], [3] mismatches over all bit patterns (zeros, denormals, infinities, negatives and NaNs
+ *        are expected here: those inputs never reach the fast path).
+ */
+int rt_selftest_exact_math(uint64_t* counts_dev, void* cuda_stream);
 
 /*
  * Gradient centralization (adamw.py:179-184): out[r] = mean over row r of g, fp32, for a
@@ -282,6 +305,10 @@ typedef struct rt_offload_cfg {
                               that consecutive tensors overlap in the pipeline */
   void* staging;        /* device memory */
   int64_t staging_bytes;
+  const float* row_mean; /* gradient centralization (adamw.py:179-184): device array of the row means of
+                            the WHOLE gradient (rt_row_means), required when hyper->centralization != 0,
+                            else NULL */
+  int64_t row_len;      /* elements per row of row_mean; 0 = the whole tensor is one row */
 } rt_offload_cfg;
 
 int64_t rt_offload_staging_bytes(int64_t chunk_elems, int ring_depth, int p_dtype,

@@ -90,7 +90,8 @@ def use_all_cores() -> int:
     return num_threads()
 
 
-def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, shared_draws=False) -> Hyper:
+def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, shared_draws=False,
+               reference_order=False) -> Hyper:
     """Per-step scalars exactly as adamw.py:173-188 forms them (Python doubles), each rounded
     once to fp32 where ATen would cast the Python scalar to the tensor's dtype."""
     beta1, beta2 = betas
@@ -109,7 +110,7 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, shared_dr
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
-    h.flags = 2 if shared_draws else 0
+    h.flags = (2 if shared_draws else 0) | (4 if reference_order else 0)
     h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 

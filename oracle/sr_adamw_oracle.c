@@ -143,11 +143,21 @@ int rto_adamw_sr(void* p, const void* g, void* m, void* v, int64_t n,
     float m1 = fmaf(h->one_minus_beta1, gi, mi * h->beta1);
     /* ema_sq.mul_(beta2).addcmul_(grad, grad, value=1-beta2) (adamw.py:191) */
     float v1 = fmaf(h->one_minus_beta2 * gi, gi, vi * h->beta2);
-    /* denom = (sqrt(v) / bias_correction_sqrt).add_(eps) (adamw.py:193-195) */
-    float den = sqrtf(v1) / h->bias_correction2_sqrt + h->eps;
-    /* p.mul_(1 - step_size*wd); p.addcdiv_(m, denom, value=-step_size) (adamw.py:197-200) */
+    /* p.mul_(1 - step_size*wd) (adamw.py:197-198) */
     float pw = h->apply_decay ? pi * h->decay : pi;
-    float p1 = pw + (h->neg_step_size * m1) / den;
+    float p1;
+    if (h->flags & RT_HYPER_REFERENCE_ORDER) {
+      /* denom = (sqrt(v) / bias_correction_sqrt).add_(eps) (adamw.py:193-195);
+       * p.addcdiv_(m, denom, value=-step_size) (adamw.py:199-200), in the reference's order */
+      float den = sqrtf(v1) / h->bias_correction2_sqrt + h->eps;
+      p1 = pw + (h->neg_step_size * m1) / den;
+    } else {
+      /* the same two lines in the default order of include/rt_b200.h: the division by the bias
+       * correction becomes a multiply-add, the division by denom a reciprocal and a multiply-add;
+       * sqrtf, fmaf and 1.0f / x are correctly rounded here as on the GPU */
+      float den = fmaf(sqrtf(v1), h->inv_bias_correction2_sqrt, h->eps);
+      p1 = fmaf(h->neg_step_size * m1, 1.0f / den, pw);
+    }
     if (f32_p) f32_p[i] = p1;
     if (f32_m) f32_m[i] = m1;
     if (f32_v) f32_v[i] = v1;

@@ -30,8 +30,8 @@ class Hyper(ctypes.Structure):
                 ("inv_bias_correction2_sqrt", ctypes.c_float), ("reserved", c_uint32 * 3)]
 
 
-HYPER_FAST_MATH = 1
 HYPER_SHARED_DRAWS = 2
+HYPER_REFERENCE_ORDER = 4
 
 
 class Debug(ctypes.Structure):
@@ -49,7 +49,8 @@ class TensorDesc(ctypes.Structure):
 
 class OffloadCfg(ctypes.Structure):
     _fields_ = [("chunk_elems", c_int64), ("ring_depth", c_int), ("defer_join", c_int),
-                ("staging", c_void_p), ("staging_bytes", c_int64)]
+                ("staging", c_void_p), ("staging_bytes", c_int64),
+                ("row_mean", c_void_p), ("row_len", c_int64)]
 
 
 MAX_PEERS = 15
@@ -79,6 +80,7 @@ _SIGNATURES = {
     "rt_adamw_sr_flat": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                  ctypes.POINTER(Hyper), c_uint64, c_uint32, c_int64, c_void_p, c_int64,
                                  ctypes.POINTER(Debug), c_void_p]),
+    "rt_selftest_exact_math": (c_int, [c_void_p, c_void_p]),
     "rt_row_means": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "rt_plan_create": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(TensorDesc), c_int64, c_int]),
     "rt_plan_destroy": (c_int, [c_void_p]),
@@ -126,7 +128,7 @@ def check(rc: int, what: str = "librt_b200") -> None:
         raise kind(f"{what} failed ({rc}): {msg}")
 
 
-def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math=False,
+def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, reference_order=False,
                shared_draws=False) -> Hyper:
     """The per-step scalars of ``adamw.py:173-188``: Python-double arithmetic written the way the
     reference writes it, then one rounding to fp32 each (what ATen does when a Python scalar
@@ -145,7 +147,7 @@ def make_hyper(lr, betas, eps, weight_decay, step, centralization=0.0, fast_math
     h.centralization = centralization
     h.apply_decay = 1 if weight_decay != 0 else 0
     h.step = step
-    h.flags = (HYPER_FAST_MATH if fast_math else 0) | (HYPER_SHARED_DRAWS if shared_draws else 0)
+    h.flags = (HYPER_REFERENCE_ORDER if reference_order else 0) | (HYPER_SHARED_DRAWS if shared_draws else 0)
     h.inv_bias_correction2_sqrt = 1.0 / float(ctypes.c_float(bias_correction_sqrt).value)
     return h
 

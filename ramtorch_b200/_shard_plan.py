@@ -227,6 +227,33 @@ _PUSH_BUCKETS: Dict[int, List[Bucket]] = {}   # cuda device index -> buckets wit
 _PULL_BUCKETS: Dict[int, List[Bucket]] = {}   # cuda device index -> buckets with peer-mapped gradients
 
 
+def release_plan(rank_param_groups) -> None:
+    """Forget the flat buffers of a ``rank -> groups`` dict: its peer-mapped buckets leave the
+    registries the optimizer consults, so their memory is returned once the parameters that view
+    them are gone.  For programs that build several sharded parameter sets one after another; the
+    dict must not be used with ``broadcast_zero_params`` / the ZeRO-2 hooks afterwards."""
+    plan = getattr(rank_param_groups, "plan", None)
+    if plan is None:
+        hit = _PLANS.pop(id(rank_param_groups), None)
+        plan = hit[1] if hit is not None else None
+    if plan is None:
+        return
+    for b in plan.buckets.values():
+        for registry in (_PUSH_BUCKETS, _PULL_BUCKETS):
+            for index in list(registry):
+                registry[index] = [x for x in registry[index] if x is not b]
+                if not registry[index]:
+                    del registry[index]
+        b.symm = b.gsymm = None
+        b.peer_ptrs = b.gpeer_ptrs = None
+        b.flat = b.gflat = None
+        b.grad_views = []
+    try:
+        rank_param_groups.plan = None
+    except AttributeError:
+        pass
+
+
 def pull_bucket_for(device_index: int, grad_ptrs) -> Optional[Bucket]:
     """The peer-mapped gradient bucket on ``device_index`` that holds most of the given addresses."""
     best, best_hits = None, 0

@@ -92,7 +92,9 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
                                    const rt_offload_cfg* cfg, void* cuda_stream) {
   if (int rc = validate_flat(p, g, m, v, n, p_dtype, g_dtype, state_dtype, hyper, 0)) return rc;
   if (!cfg) return fail(RT_E_NULL, "cfg must be non-null");
-  if (hyper->centralization != 0.0f) return fail(RT_E_CONFIG, "centralization is not supported on the streamed path");
+  if (hyper->centralization != 0.0f && !cfg->row_mean)
+    return fail(RT_E_CONFIG, "centralization != 0 needs cfg->row_mean (the row means of the whole gradient, see rt_row_means)");
+  if (cfg->row_len < 0 || cfg->row_len > 0xFFFFFFFFll) return fail(RT_E_SIZE, "row_len must fit 32 bits");
   const int64_t chunk = cfg->chunk_elems > 0 ? cfg->chunk_elems : (int64_t)16 << 20;
   const int depth = cfg->ring_depth > 0 ? cfg->ring_depth : 3;
   if ((chunk & 7) || depth < 2 || depth > kMaxDepth) return fail(RT_E_CONFIG, "chunk_elems must be a multiple of 8 and ring_depth in 2..8");
@@ -179,12 +181,14 @@ extern "C" int rt_adamw_sr_offload(void* p, const void* g, void* m, void* v, int
     t.m = sm ? (void*)sm : (void*)(static_cast<char*>(m) + off * ss);
     t.v = sv ? (void*)sv : (void*)(static_cast<char*>(v) + off * ss);
     t.numel = len;
-    t.index0 = off;
+    t.index0 = off;      // also what finds a chunk's rows in row_mean
     t.tensor_id = tensor_id;
+    t.row_mean = hyper->centralization != 0.0f ? cfg->row_mean : nullptr;
+    t.row_len = (uint32_t)cfg->row_len;
     t.flags = vec_flag(t.p, t.g, t.m, t.v);
+    const int64_t nblocks = set_cta_shift(t, len, p_dtype, g_dtype, state_dtype);
     if (int rc = launch_adamw(p_dtype, g_dtype, state_dtype, nullptr, nullptr, nullptr, t, *hyper, seed,
-                              (len + kChunkElems - 1) / kChunkElems, pipe->run,
-                              hyper->flags, nullptr, nullptr))
+                              nblocks, pipe->run, hyper->flags, nullptr, nullptr))
       return rc;
     RT_CUDA(cudaEventRecord(pipe->run_done[slot], pipe->run));
 

@@ -25,20 +25,25 @@ struct DevTensor {
   uint32_t flags;         // kVecOk
 };
 constexpr uint32_t kVecOk = 1u;  // all four pointers are 16-byte aligned
-constexpr int kChunkShiftBit = 8;  // flags bits 8..11: a CTA covers (8192 << shift) elements
-constexpr int64_t kBigLaunchChunks = 65536;       // launches with at least this many 8192-element pieces ...
+constexpr int kChunkShiftBit = 8;  // flags bits 8..11: a CTA covers (kPieceElems << shift) elements
+constexpr int64_t kBigLaunchChunks = 65536;       // launches of at least this many 8192-element chunks ...
 constexpr int64_t kLongTensorElems = 1 << 20;     // ... give tensors at least this long the longer CTAs
+constexpr int64_t kSmallLaunchElems = (int64_t)1 << 25;  // launches below this get short CTAs
+constexpr int kSmallShift = 1;                    // ... of (kPieceElems << kSmallShift) elements
 
 // Peer copies of a shared parameter region (kernel argument; n == 0 disables).
 struct PushTable {
   const char* local;          // base of the region in this GPU's memory
   int64_t bytes;
   int n;                      // number of peers
+  int order;                  // 0: peer stores after the local store, 1: before it
   char* base[RT_MAX_PEERS];   // the region's base in each peer's memory, as mapped here
 };
 
 constexpr int kThreads = 256;
-constexpr int kChunkElems = kThreads * 8 * 4;  // elements one CTA walks through
+constexpr int kPieceElems = kThreads * 8;            // one iteration of a CTA: eight elements per thread
+constexpr int kDefaultShift = 2;
+constexpr int kChunkElems = kPieceElems << kDefaultShift;  // elements a default CTA walks through (8192)
 
 // error plumbing -------------------------------------------------------------
 int fail(int code, const std::string& msg);
@@ -86,6 +91,9 @@ int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* ch
                  uint64_t seed, int64_t nblocks, cudaStream_t stream, uint32_t flags,
                  const PeerTables* peers, const HyperPack* pack);
 int check_launchable(int pd, int gd, int sd, uint32_t flags, const PeerTables* peers);
+int cta_shift(int64_t launch_elems, int64_t tensor_elems, bool all16);
+int small_shift();
+int64_t set_cta_shift(DevTensor& t, int64_t launch_elems, int pd, int gd, int sd);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);
 int validate_flat(const void* p, const void* g, const void* m, const void* v, int64_t n,

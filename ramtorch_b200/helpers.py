@@ -72,3 +72,30 @@ def reattach_is_ramtorch_flags(module: nn.Module) -> nn.Module:
             if isinstance(tensor, torch.Tensor):
                 tensor.is_ramtorch = True
     return module
+
+
+DEVICE_GRAD_ATTR = "rt_device_grad"
+
+
+def accumulate_device_grad(param: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+    """Producer side of the gradient hand-off for CPU-resident (``is_ramtorch``) parameters.
+
+    The reference's ``Linear`` backward copies each weight gradient to host memory
+    (``weight_cpu.grad = w_grad.to("cpu")``, linear.py:416-427) only for ``AdamW.step`` to copy it
+    back to the GPU (adamw.py:167).  A backward that calls this instead leaves the gradient in HBM:
+    the first micro-batch stores it on the parameter as ``rt_device_grad``, later ones add to it in
+    place (what ``Tensor.grad`` accumulation does; PyTorch itself refuses a CUDA ``.grad`` on a CPU
+    tensor), ``AdamW.step`` consumes it in preference to ``p.grad`` and ``AdamW.zero_grad`` clears
+    it.  ``grad`` must be a CUDA tensor of the parameter's shape that the caller will not reuse (or
+    a clone).  Returns the accumulated gradient."""
+    if not grad.is_cuda:
+        raise ValueError("accumulate_device_grad is for gradients that live in HBM")
+    if grad.shape != param.shape:
+        raise ValueError("gradient and parameter shapes differ")
+    held = param.__dict__.get(DEVICE_GRAD_ATTR)
+    if held is None:
+        held = grad.detach()
+        setattr(param, DEVICE_GRAD_ATTR, held)
+    else:
+        held.add_(grad.detach())
+    return held

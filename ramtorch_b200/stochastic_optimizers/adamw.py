@@ -203,9 +203,18 @@ class AdamW(Optimizer):
         offload_chunk_elems: elements per streamed chunk for host-resident tensors.
         offload_ring_depth: staging slots of the streaming pipeline (2..8).
         sync: wait for the step to finish before returning, as the reference does (default True).
-        fast_math: approximate square root and reciprocal in the parameter update (moments stay
-            exact); results stay within 1e-6 relative of the exact update but are no longer
-            bit-identical to the CPU checker (default False).
+        reference_order: form the denominator and the quotient in the reference's own operation
+            order (``sqrt(v)/bc + eps`` and ``p + (a*m)/den``: two IEEE divisions per element)
+            instead of the default ``fma(sqrt(v), 1/bc, eps)`` and ``fma(a*m, 1/den, p)``.  Both
+            are reproducible bit for bit by the CPU checker; the moments are identical either
+            way and the parameters agree within 1e-6 (default False).
+        register_host_memory: pin, in place (``cudaHostRegister``), host-resident parameters and
+            moments whose storage is shared memory and not page-locked -- parameter storage shared
+            between worker processes through ``mp.spawn`` pickling arrives like that in the worker
+            -- so that their copies overlap with the update instead of falling back to pageable
+            transfers.  The registration lasts until ``release_host_memory()`` or until the
+            optimizer is collected; gradients are never registered (they are usually re-allocated
+            by every backward).  Default True.
         shared_draws: one Philox block per eight elements serves parameter and both moments
             (lanes rotated by two per stream) instead of three independent blocks.  Every rounding
             still sees a uniform 16-bit draw, the three roundings of any one element stay mutually
@@ -218,7 +227,7 @@ class AdamW(Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2,
                  centralization=0, chunk_size=64, dtype=torch.bfloat16, storage_device="cpu",
                  *, seed=0, offload_chunk_elems=1 << 24, offload_ring_depth=3, sync=True,
-                 fast_math=False, shared_draws=True):
+                 reference_order=False, shared_draws=True, register_host_memory=True):
         if dtype not in N.DTYPE_CODE:
             raise ValueError(f"unsupported state dtype {dtype}: bf16, fp32 or fp16")
         if offload_chunk_elems <= 0 or offload_chunk_elems % 8:
@@ -239,8 +248,10 @@ class AdamW(Optimizer):
         self.offload_chunk_elems = int(offload_chunk_elems)
         self.offload_ring_depth = int(offload_ring_depth)
         self.sync = bool(sync)
-        self.fast_math = bool(fast_math)
+        self.reference_order = bool(reference_order)
         self.shared_draws = bool(shared_draws)
+        self.register_host_memory = bool(register_host_memory)
+        self._registered = {}   # storage address -> bytes pinned in place by this optimizer
         self._plans = {}      # cuda device index -> _DevicePlan
         self._staging = {}    # cuda device index -> uint8 tensor
         self._row_scratch = {}  # cuda device index -> fp32 row means for centralization
@@ -311,6 +322,55 @@ class AdamW(Optimizer):
                 st["ema"] = torch.zeros(p.shape, dtype=dtype, device=dev)
                 st["ema_squared"] = torch.zeros(p.shape, dtype=dtype, device=dev)
 
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        """``Optimizer.zero_grad`` plus the device-side gradients of CPU parameters
+        (``p.rt_device_grad``, see ``helpers.accumulate_device_grad``): dropped, or zeroed in place
+        with ``set_to_none=False``, exactly like ``p.grad``."""
+        super().zero_grad(set_to_none=set_to_none)
+        for group in self.param_groups:
+            for p in group["params"]:
+                g = p.__dict__.get(DEVICE_GRAD_ATTR)
+                if g is not None:
+                    if set_to_none:
+                        setattr(p, DEVICE_GRAD_ATTR, None)
+                    else:
+                        g.zero_()
+
+    def _pin_in_place(self, lib, t: torch.Tensor) -> bool:
+        """Page-lock the storage of a host tensor where it lies (``rt_host_register``); True when the
+        storage is pinned afterwards."""
+        # Only storages in shared memory qualify: they are mappings of their own (page-aligned, no
+        # neighbours), and they are the case that needs it.  Page-locking a few bytes in the middle
+        # of the malloc heap would also lock whatever shares their pages, and a later copy from a
+        # buffer that straddles locked and unlocked pages is refused by the CUDA runtime.
+        if not self.register_host_memory or not t.is_shared():
+            return False
+        storage = t.untyped_storage()
+        ptr, nbytes = storage.data_ptr(), storage.nbytes()
+        if ptr in self._registered:
+            return True
+        if nbytes == 0 or lib.rt_host_register(ptr, nbytes) != 0:
+            return False
+        self._registered[ptr] = nbytes
+        return True
+
+    def __del__(self):   # the pages must not stay locked once nobody streams them any more
+        try:
+            self.release_host_memory()
+        except Exception:  # pragma: no cover - interpreter shutdown
+            pass
+
+    def release_host_memory(self) -> None:
+        """Undo the in-place pinning done by ``register_host_memory`` (after a device synchronise:
+        no copy may still be using the pages)."""
+        if not getattr(self, "_registered", None):
+            return
+        torch.cuda.synchronize()
+        lib = N.lib()
+        for ptr in list(self._registered):
+            lib.rt_host_unregister(ptr)
+            del self._registered[ptr]
+
     def _staging_for(self, index: int, nbytes: int) -> torch.Tensor:
         buf = self._staging.get(index)
         if buf is None or buf.numel() < nbytes:
@@ -356,6 +416,7 @@ class AdamW(Optimizer):
         streamed = []   # (device index, p, grad, ema, ema_sq, tensor_id, hyper_index)
         hyper_rows, hyper_index = [], {}
         centered = {}   # device index -> {position in resident[index]: number of rows}
+        centered_streamed = {}   # position in streamed: number of rows
         skipped_empty = False
         late = []
         stepped = []    # state dicts whose counter advances with this step
@@ -384,7 +445,7 @@ class AdamW(Optimizer):
                     hi = hyper_index[key] = len(hyper_rows)
                     hyper_rows.append(N.make_hyper(group["lr"], group["betas"], group["eps"],
                                                    group["weight_decay"], t,
-                                                   group["centralization"], self.fast_math, self.shared_draws))
+                                                   group["centralization"], self.reference_order, self.shared_draws))
                 ema, ema_sq = state["ema"], state["ema_squared"]
                 pd = p.data
                 if pd.numel() == 0:
@@ -420,8 +481,7 @@ class AdamW(Optimizer):
                         centered.setdefault(index, {})[len(resident[index]) - 1] = rows
                 else:
                     if group["centralization"] != 0:
-                        raise NotImplementedError("centralization != 0 needs parameter, gradient and moments "
-                                                  "on the GPU (it is not available on the streamed path)")
+                        centered_streamed[len(streamed)] = pd.shape[0] if pd.dim() >= 2 else 1
                     if grad.is_cuda and SP.pull_bucket_for(index, [grad.data_ptr()]) is not None:
                         raise RuntimeError("ZeRO-2 fused gradient reduction (RT_ZERO2_FUSED_PULL=1) needs the moments in "
                                            "HBM (storage_device on the GPU): the streamed path does not sum the ranks' "
@@ -453,27 +513,46 @@ class AdamW(Optimizer):
         # one staging ring per device, sized for the largest streamed tensor of this step, so that
         # all of them share its geometry and follow each other through the pipeline
         jobs, ring_bytes = [], {}
-        for index, pd, grad, ema, ema_sq, tid, hi in streamed:
-            host = [not t.is_cuda for t in (pd, grad, ema, ema_sq)]
-            if not self._warned_pageable:
-                for t, h in zip((pd, grad, ema, ema_sq), host):
-                    if h and not t.is_pinned():
-                        warnings.warn("a host-resident tensor is not pinned: its copies fall back to "
+        for pos, (index, pd, grad, ema, ema_sq, tid, hi) in enumerate(streamed):
+            row_mean = None
+            rows = centered_streamed.get(pos)
+            if rows is not None:
+                # Gradient centralization (adamw.py:179-184) needs the row means before the first
+                # chunk is updated: one pass over g alone.  A host-resident gradient is brought to the
+                # device whole for that pass and the step then reads it there, so it crosses the
+                # link once, as it would without centralization.
+                with torch.cuda.device(index):
+                    if not grad.is_cuda:
+                        grad = grad.to(torch.device("cuda", index), non_blocking=True)
+                        self._keepalive.append(grad)
+                    row_len = grad.numel() // rows
+                    means = torch.empty(rows, dtype=torch.float32, device=grad.device)
+                    self._keepalive.append(means)
+                    N.check(lib.rt_row_means(grad.data_ptr(), N.DTYPE_CODE[grad.dtype], rows, row_len,
+                                             means.data_ptr(), N.stream_ptr(index)), "rt_row_means")
+                    row_mean = (means.data_ptr(), row_len if rows > 1 else 0)
+            tensors = (pd, grad, ema, ema_sq)
+            host = [not t.is_cuda for t in tensors]
+            for t, h, what in zip(tensors, host, ("parameter", "gradient", "moment", "moment")):
+                if h and not t.is_pinned() and not (what != "gradient" and self._pin_in_place(lib, t)):
+                    if not self._warned_pageable:
+                        warnings.warn(f"a host-resident {what} is not pinned: its copies fall back to "
                                       "pageable transfers and do not overlap; pin it for full speed")
                         self._warned_pageable = True
-                        break
             codes = (N.DTYPE_CODE[pd.dtype], N.DTYPE_CODE[grad.dtype], N.DTYPE_CODE[ema.dtype])
             chunk = min(self.offload_chunk_elems, (pd.numel() + 7) // 8 * 8)
             need = lib.rt_offload_staging_bytes(chunk, self.offload_ring_depth, *codes, *map(int, host))
             if need < 0:
                 N.check(int(need), "rt_offload_staging_bytes")
             ring_bytes[index] = max(ring_bytes.get(index, 256 * self.offload_ring_depth), int(need))
-            jobs.append((index, pd, grad, ema, ema_sq, tid, hi, codes, chunk))
-        for index, pd, grad, ema, ema_sq, tid, hi, codes, chunk in jobs:
+            jobs.append((index, pd, grad, ema, ema_sq, tid, hi, codes, chunk, row_mean))
+        for index, pd, grad, ema, ema_sq, tid, hi, codes, chunk, row_mean in jobs:
             used.add(index)
             with N.trace("rt.step.streamed"), torch.cuda.device(index):
                 staging = self._staging_for(index, ring_bytes[index])
                 cfg = N.OffloadCfg(chunk, self.offload_ring_depth, 1, staging.data_ptr(), staging.numel())
+                if row_mean is not None:
+                    cfg.row_mean, cfg.row_len = row_mean
                 N.check(lib.rt_adamw_sr_offload(pd.data_ptr(), grad.data_ptr(), ema.data_ptr(),
                                                 ema_sq.data_ptr(), pd.numel(), *codes,
                                                 ctypes.byref(hyper_arr[hi]), seed, tid,
@@ -582,7 +661,7 @@ class AdamW(Optimizer):
         for gi, step in f["classes"]:
             g = groups[gi]
             rows.append(N.make_hyper(g["lr"], g["betas"], g["eps"], g["weight_decay"], step + 1,
-                                     g["centralization"], self.fast_math, self.shared_draws))
+                                     g["centralization"], self.reference_order, self.shared_draws))
         hyper_arr = (N.Hyper * len(rows))(*rows)
         gptrs = np.fromiter(map(torch.Tensor.data_ptr, grads), dtype=np.uint64, count=len(grads))
         index = f["index"]

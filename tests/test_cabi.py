@@ -30,7 +30,7 @@ def test_struct_sizes_match_header():
     assert ctypes.sizeof(N.Hyper) == 64
     assert ctypes.sizeof(N.TensorDesc) == 72
     assert ctypes.sizeof(N.Debug) == 48
-    assert ctypes.sizeof(N.OffloadCfg) == 32
+    assert ctypes.sizeof(N.OffloadCfg) == 48
     assert ctypes.sizeof(N.Stats) == 40
 
 

@@ -67,12 +67,12 @@ def test_step_fails_loudly_without_a_cuda_device():
 @pytest.mark.parametrize("wd", [0.0, 0.01])
 def test_native_and_checker_scalars_are_identical(step, wd):
     for shared in (False, True):
-        a = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, wd, step, shared_draws=shared)
-        b = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, wd, step, shared_draws=shared)
-        assert bytes(a) == bytes(b)
-    fast = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, wd, step, fast_math=True)
-    assert fast.flags == N.HYPER_FAST_MATH
-    assert abs(fast.inv_bias_correction2_sqrt * fast.bias_correction2_sqrt - 1) < 1e-6
+        for ref in (False, True):
+            a = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, wd, step, shared_draws=shared, reference_order=ref)
+            b = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, wd, step, shared_draws=shared, reference_order=ref)
+            assert bytes(a) == bytes(b)
+            assert a.flags == (N.HYPER_SHARED_DRAWS if shared else 0) | (N.HYPER_REFERENCE_ORDER if ref else 0)
+    assert abs(a.inv_bias_correction2_sqrt * a.bias_correction2_sqrt - 1) < 1e-6
 
 
 def test_device_gradient_attribute_only_applies_to_cpu_parameters():

@@ -217,26 +217,34 @@ def test_copy_stochastic_drop_in():
     assert (to_numpy(dst) == oracle.sr_round_bf16(src.cpu().numpy(), r)).all()
 
 
+@pytest.mark.parametrize("where", ["all-in-hbm", "moments-on-host", "everything-on-host"])
 @pytest.mark.parametrize("name", ["step_bf16_centralized_2d.npz", "step_bf16_centralized_1d.npz"])
-def test_centralization_through_the_optimizer_against_the_reference_fixture(name):
+def test_centralization_through_the_optimizer_against_the_reference_fixture(name, where):
     """adamw.py:179-184 via ``AdamW(centralization=c)``: one step from the recorded inputs lands
     within the fp32 tolerance of what the reference produced (its row means are summed in another
-    order, so bit equality is not expected)."""
+    order, so bit equality is not expected).  With the reference's default ``storage_device="cpu"``
+    the moments, and in the last case parameter and gradient too, are streamed in chunks much
+    shorter than the tensor: the row means come from a pass over the whole gradient first."""
     from ramtorch_b200 import AdamW
     from util import TORCH_DT, load_golden, to_torch
     d = load_golden(name)
     meta = d["meta"]
-    dev = torch.device("cuda")
+    dev = torch.device("cuda") if where != "everything-on-host" else torch.device("cpu")
     shape = tuple(meta["shape"])
     p = to_torch(d["in_p"], meta["p_dtype"], dev).reshape(shape)
     p.grad = to_torch(d["in_g"], meta["g_dtype"], dev).reshape(shape)
+    if where == "everything-on-host":
+        p, g = p.pin_memory(), p.grad.pin_memory()
+        p.grad = g
     opt = AdamW([p], lr=meta["lr"], betas=tuple(meta["betas"]), eps=meta["eps"], weight_decay=meta["weight_decay"],
-                centralization=meta["centralization"], dtype=TORCH_DT[meta["state_dtype"]], storage_device="cuda")
+                centralization=meta["centralization"], dtype=TORCH_DT[meta["state_dtype"]],
+                storage_device="cuda" if where == "all-in-hbm" else "cpu", offload_chunk_elems=1024)
     st = opt.state[p]
     st["ema"].copy_(to_torch(d["in_m"], meta["state_dtype"], dev).reshape(shape))
     st["ema_squared"].copy_(to_torch(d["in_v"], meta["state_dtype"], dev).reshape(shape))
     st["step"] = meta["step"] - 1
     opt.step()
+    assert opt.last_step_info["streamed"] == (0 if where == "all-in-hbm" else 1)
     # compare with the reference's recorded tensors after the step: bf16 results within one step,
     # fp32 moments within 1e-6 of the update's scale
     for got_t, key in ((p, "out_p"), (st["ema"], "out_m"), (st["ema_squared"], "out_v")):
@@ -410,3 +418,142 @@ def test_streamed_call_rejects_a_short_staging_buffer_before_copying_anything():
     assert after == before
     torch.cuda.synchronize()
     assert float(p.float().abs().sum()) == 0 and float(m.float().abs().sum()) == 0
+
+
+def test_streamed_centralized_step_is_bit_identical_to_the_resident_one():
+    """Same tensors, same seed: centralization through the chunked host pipeline (moments pinned on
+    the host, chunks that cut rows in the middle) gives exactly the resident result."""
+    from ramtorch_b200 import AdamW
+    shapes = [(257, 130), (1000,), (64, 3, 5)]
+    results = []
+    for storage in ("cuda", "cpu"):
+        params = make_params(shapes, torch.bfloat16, "cuda")
+        opt = AdamW(params, centralization=0.5, dtype=torch.bfloat16, storage_device=storage, seed=12,
+                    offload_chunk_elems=4096, **HP)
+        for s in range(3):
+            for p, g in zip(params, make_grads(shapes, torch.bfloat16, s)):
+                p.grad = g.cuda()
+            opt.step()
+        results.append([to_numpy(p) for p in params] + [to_numpy(opt.state[p]["ema_squared"]) for p in params])
+    for a, b in zip(*results):
+        assert bits_equal(a, b) == 0
+
+
+def test_load_state_dict_in_place_after_the_fast_path_is_armed():
+    """Two steps arm the repeat-step cache; load_state_dict() then swaps every state dict and tensor.
+    The following steps must use the loaded moments and counters, not the cached ones."""
+    import copy
+    from ramtorch_b200 import AdamW
+    shapes = SHAPES[:6]
+    params = make_params(shapes, torch.bfloat16, "cuda")
+    opt = AdamW(params, dtype=torch.bfloat16, storage_device="cuda", seed=9, **HP)
+    mirror = Mirror(params, torch.bfloat16, 9, **HP)
+
+    def run(step_seed):
+        grads = make_grads(shapes, torch.bfloat16, step_seed)
+        for p, g in zip(params, grads):
+            p.grad = g.cuda()
+        opt.step()
+        mirror.apply(grads)
+
+    run(0)
+    snapshot = copy.deepcopy(opt.state_dict())                       # state after step 1 ...
+    kept = ([a.copy() for a in mirror.m], [a.copy() for a in mirror.v], list(mirror.step))
+    run(1); run(2)
+    assert opt.last_step_info.get("fast")                            # ... the cache is armed by now
+    opt.load_state_dict(snapshot)                                     # back to the moments of step 1
+    mirror.m, mirror.v, mirror.step = kept
+    run(3)
+    assert not opt.last_step_info.get("fast")
+    check(opt, params, mirror)
+    run(4)
+    check(opt, params, mirror)
+    # an in-place edit of a counter is noticed too
+    run(5)
+    assert opt.last_step_info.get("fast")
+    opt.state[params[0]]["step"] = 40
+    mirror.step[0] = 40
+    run(6)
+    check(opt, params, mirror)
+
+
+def test_a_rejected_step_leaves_every_counter_where_it_was():
+    from ramtorch_b200 import AdamW
+    params = make_params([(64,), (4, 32)], torch.bfloat16, "cuda")
+    params[1] = params[1].t()                                  # a non-contiguous parameter is refused
+    opt = AdamW(params, dtype=torch.bfloat16, storage_device="cuda", **HP)
+    for p in params:
+        p.grad = torch.zeros(p.shape, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="contiguous"):
+        opt.step()
+    assert [opt.state[p]["step"] for p in params] == [0, 0]
+
+
+def _shared_storage_owner(weight, grad, seed):
+    """Child process = the owning rank: steps the shared CPU weight through the streamed path."""
+    from ramtorch_b200 import AdamW
+    torch.cuda.set_device(0)
+    assert weight.is_shared() and not weight.is_pinned()
+    weight.is_ramtorch = True
+    weight.grad = grad
+    opt = AdamW([weight], dtype=torch.bfloat16, seed=seed, offload_chunk_elems=8192, **HP)
+    opt.step()
+    assert weight.is_pinned()                      # re-pinned in place by the optimizer (rt_host_register)
+    assert opt.last_step_info["streamed"] == 1
+    opt.release_host_memory()
+
+
+def test_shared_cpu_parameter_storage_is_repinned_and_updated_in_place_for_the_other_ranks():
+    """Parameter consumption after the step (linear.py:168-188 reads ``weight_cpu`` again; the
+    workers share its storage through ``mp.spawn`` pickling, README.md:177-182): the owner's step
+    writes the new values into the shared pages, so a process that never ran the optimizer sees
+    them without any redistribution (zero1.py:81 skips such parameters).  In the worker the storage
+    arrives unpinned; the optimizer page-locks it where it lies."""
+    import torch.multiprocessing as mp
+    n, seed = 50001, 17
+    weight = make_params([(n,)], torch.bfloat16, "cpu")[0].share_memory_()
+    grad = make_grads([(n,)], torch.bfloat16, 0)[0].share_memory_()
+    before = to_numpy(weight).copy()
+    ctx = mp.get_context("spawn")
+    child = ctx.Process(target=_shared_storage_owner, args=(weight, grad, seed))
+    child.start()
+    child.join(timeout=300)
+    assert child.exitcode == 0
+    want, m, v = before.copy(), np.zeros(n, np.uint16), np.zeros(n, np.uint16)
+    oracle.adamw_sr(want, to_numpy(grad), m, v, oracle.BF16, oracle.BF16, oracle.BF16,
+                    oracle.make_hyper(HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"], 1, shared_draws=True),
+                    seed=seed, tensor_id=0)
+    got = to_numpy(weight)                          # read by this process, which ran no optimizer
+    assert bits_equal(got, want) == 0 and bits_equal(got, before) > 0
+
+
+def test_gradient_producer_keeps_micro_batch_gradients_in_hbm():
+    """Stand-in for the patched ``Linear`` backward (linear.py:401-430): instead of copying each
+    weight gradient to the host it calls ``accumulate_device_grad``.  Over two micro-batches the
+    gradient accumulates in HBM, ``step`` consumes it without moving gradient bytes over the link,
+    ``zero_grad`` clears it, and the result equals a host-side accumulation."""
+    from ramtorch_b200 import AdamW, _native as N
+    from ramtorch_b200.helpers import accumulate_device_grad
+    shapes = [(4099,), (64, 33)]
+    params = make_params(shapes, torch.bfloat16, "cpu", pin=True)
+    opt = AdamW(params, dtype=torch.bfloat16, **HP, seed=4, offload_chunk_elems=32768)
+    mirror = Mirror(params, torch.bfloat16, 4, **HP)
+    for s in range(2):
+        micro = [make_grads(shapes, torch.bfloat16, 10 * s + k) for k in range(2)]
+        for batch in micro:                                   # "backward" of each micro-batch
+            for p, g in zip(params, batch):
+                accumulate_device_grad(p, g.cuda())
+        total = [a + b for a, b in zip(*micro)]               # bf16 accumulation, as Tensor.grad would
+        for p, t in zip(params, total):
+            assert p.grad is None and torch.equal(p.rt_device_grad.cpu(), t)
+        before = N.stats()["h2d_bytes"]
+        opt.step()
+        assert N.stats()["h2d_bytes"] - before == sum(6 * p.numel() for p in params)
+        mirror.apply(total)
+        check(opt, params, mirror)
+        opt.zero_grad()
+        assert all(p.rt_device_grad is None for p in params)
+    for p, g in zip(params, make_grads(shapes, torch.bfloat16, 99)):
+        accumulate_device_grad(p, g.cuda())
+    opt.zero_grad(set_to_none=False)
+    assert all(float(p.rt_device_grad.abs().sum()) == 0 for p in params)

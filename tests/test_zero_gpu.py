@@ -109,6 +109,38 @@ def _single_process(world, exact=True, fp32_sum=False):
     return [p.detach().float().cpu() for p in params]
 
 
+def _collect(out, procs, deadline_s=300.0):
+    """One report per worker, or a failure naming the workers that died or ran out of time: a
+    worker that exits before reporting must not leave the test waiting on the queue forever."""
+    import queue
+    import time
+    results, t_end = [], time.monotonic() + deadline_s
+    while len(results) < len(procs):
+        try:
+            results.append(out.get(timeout=2.0))
+            continue
+        except queue.Empty:
+            pass
+        reported = {r[0] for r in results}
+        dead = [k for k, p in enumerate(procs) if not p.is_alive() and k not in reported]
+        if dead or time.monotonic() > t_end:
+            try:                                  # a report may have arrived between the two checks
+                while True:
+                    results.append(out.get(timeout=1.0))
+            except queue.Empty:
+                pass
+            reported = {r[0] for r in results}
+            missing = [k for k in range(len(procs)) if k not in reported]
+            if not missing:
+                break
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            why = "exited without reporting" if dead else f"did not report within {deadline_s:.0f} s"
+            pytest.fail(f"workers {missing} {why} (exit codes {[procs[k].exitcode for k in missing]})")
+    return sorted(results, key=lambda r: r[0])
+
+
 @pytest.mark.parametrize("mode,exact", [("peer-push", True), ("all-gather", True), ("peer-push+grad-pull", True),
                                         ("peer-push+grad-pull", False)])
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -116,14 +148,14 @@ def test_zero_loop_matches_single_process(world, mode, exact):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
-    out = ctx.SimpleQueue()
+    out = ctx.Queue()
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     procs = [ctx.Process(target=_worker, args=(r, world, port, out, mode, exact)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted((out.get() for _ in procs), key=lambda r: r[0])
+    results = _collect(out, procs)
     for p in procs:
         p.join(timeout=120)
     want = _single_process(world, exact, fp32_sum=(mode == "peer-push+grad-pull"))
