@@ -97,8 +97,12 @@ typedef struct rt_hyper {
 /* One Philox block per eight elements instead of three: the block of stream 0 also serves
  * the moments, read two lanes further per stream -- element i of stream s takes draw
  * ((i & 7) + 2*s) & 7 of the block of its group.  Each rounding still sees a uniform 16-bit
- * draw and stays unbiased; what is given up is independence between the rounding of p[i],
- * ema[i-2] and ema_squared[i-4] inside one group of eight.  (The reference shares one stream
+ * draw and stays unbiased, and the three roundings of any ONE element use three different
+ * draws.  What is given up is independence between the rounding of p[i], ema[i-2] and
+ * ema_squared[i-4] inside one group of eight: they compare one and the same 16-bit number with
+ * their own thresholds, so their round-up events are nested, with correlation
+ * (min(fa, fb) - fa fb) / sqrt(fa (1 - fa) fb (1 - fb)) for discarded fractions fa and fb (1 when
+ * the fractions are equal; measured to that formula in the tests).  (The reference shares one stream
  * between ALL tensors of a step, adamw.py:206-218.)  Results remain bit-identical to the CPU
  * checker run with the same flag.  Only matters when the moments are bf16.  (The Python AdamW
  * sets it unless told otherwise; at this ABI nothing is set by default.) */
@@ -272,7 +276,11 @@ int rt_plan_set_pull(rt_plan* plan, const rt_pull* pull);
  *   every tensor is a multiple of 8192 long).
  *
  * The first call on a device looks up the array's device address (with that device
- * current); make that first call before starting any stream capture.  All calls on a device
+ * current); make that first call before starting any stream capture.  That first call, and the
+ * first use of each dtype combination on a device, also make the CUDA runtime load the code of
+ * the kernels involved, which the driver may do with allocations of its own: a caller whose
+ * allocation-free phase is strict runs one small warm-up call per combination before entering
+ * it.  From then on a call allocates nothing anywhere.  All calls on a device
  * share the one array: each call overwrites the part of the tables it uses (nothing needs
  * to start at zero), so two calls whose GPU work can overlap -- different streams without an
  * ordering between them -- race on it.  Calls on one stream are ordered and safe.

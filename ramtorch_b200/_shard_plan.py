@@ -25,6 +25,29 @@ import torch
 import torch.distributed as dist
 
 ALIGN_BYTES = 256
+PARAM_IDS_KEY = "rt_param_ids"
+
+
+def grad_bucket_bytes() -> int:
+    """Target size of one gradient sub-bucket (bytes of flat buffer, all ranks' parts together):
+    256 MiB unless RT_ZERO2_BUCKET_MB says otherwise.  Large enough for NCCL to run at link speed,
+    small enough that the first reduce-scatter starts early in backward."""
+    return max(256, int(float(os.environ.get("RT_ZERO2_BUCKET_MB", "256")) * (1 << 20)))
+
+
+class SubBucket:
+    """A contiguous piece of a bucket's flat gradient buffer, [rank 0's part | ... | rank W-1's part]
+    with equal parts, holding the gradients of a run of parameters that become ready at about the
+    same time in backward.  Reduced with one in-place reduce-scatter as soon as it is complete."""
+
+    __slots__ = ("start", "part", "expected", "ready", "work", "zeroed")
+
+    def __init__(self, start, part):
+        self.start, self.part = start, part       # element offset in gflat, elements per rank
+        self.expected = 0                         # parameters of this piece that take part in backward
+        self.ready = 0                            # gradients that arrived since the last reduction
+        self.work = None                          # pending reduce-scatter
+        self.zeroed = None                        # event: the other ranks' parts have been cleared again
 
 # The fused paths use plain peer loads and stores only; keep PyTorch's symmetric memory from also
 # binding the buffers to an NVLink multicast object (nothing here uses multimem, and a rank that
@@ -44,8 +67,13 @@ class Bucket:
         self.flat: Optional[torch.Tensor] = None
         self.gflat: Optional[torch.Tensor] = None
         self.grad_views: List[Optional[torch.Tensor]] = []
+        self.order: List[int] = []           # registration position of each parameter (backward runs it in reverse)
+        self.subs: List[SubBucket] = []      # pieces of gflat, in the order backward completes them
+        self.sub_of: List[int] = []          # parameter -> index into subs
+        self.goffset: List[int] = []         # element offset of each parameter's gradient inside gflat
         self.ready = 0                       # gradients accumulated since the last reduction
         self.expected = 0                    # parameters that take part in backward
+        self.side = None                     # stream that clears reduced pieces off the critical path
         # fused redistribution: `flat` is peer-mapped and the optimizer kernel stores updated
         # parameters straight into every peer's copy
         self.peer_ptrs: Optional[List[int]] = None   # base address of every rank's flat buffer
@@ -79,11 +107,17 @@ class ShardPlan:
         self.verified = False
         seen = set()
         per_owner: Dict[tuple, Dict[int, list]] = {}
+        order_of: Dict[int, tuple] = {}      # id(param) -> position in the caller's registration order
         # same iteration order as the reference (zero1.py:78-80, zero2.py:18-21): it is what keeps
         # the collectives matched across ranks
         for owner in range(self.world_size):
-            for group in rank_param_groups[owner]:
-                for p in group["params"]:
+            for gi, group in enumerate(rank_param_groups[owner]):
+                ids = group.get(PARAM_IDS_KEY)
+                for k, p in enumerate(group["params"]):
+                    # create_zero_param_groups records each parameter's global position; a hand-built
+                    # dict falls back to "round-robin inside the group", the reference's assignment
+                    order_of.setdefault(id(p), (0, int(ids[k])) if ids is not None and len(ids) == len(group["params"])
+                                        else (1, gi, k * self.world_size + owner))
                     self.owner_of[id(p)] = owner
                     if id(p) in seen:
                         continue
@@ -111,13 +145,14 @@ class ShardPlan:
                     b.params.append(p)
                     b.owner.append(owner)
                     b.offset.append(owner * b.segment + rel[id(p)])
+                    b.order.append(order_of[id(p)])
                     self.bucket_of[id(p)] = key
             self.buckets[key] = b
 
     # ------------------------------------------------------------------ layout identity
     def fingerprint(self) -> str:
         h = hashlib.sha256()
-        h.update(str(self.world_size).encode())
+        h.update(f"{self.world_size}/{grad_bucket_bytes()}".encode())
         for key in sorted(self.buckets, key=str):
             b = self.buckets[key]
             h.update(f"|{key[0].type}:{key[1]}:{b.segment}".encode())
@@ -192,6 +227,36 @@ class ShardPlan:
                     p.data = view
         self.flattened = True
 
+    def _layout_grad_pieces(self, b: Bucket) -> int:
+        """Cut the bucket's gradients into sub-buckets.  Parameters are taken in reverse registration
+        order (the order in which backward finishes them) and a piece is closed once it holds the
+        target number of bytes; inside a piece each rank's tensors are packed into that rank's part.
+        Returns the length of the flat gradient buffer in elements."""
+        esize = torch.empty((), dtype=b.dtype).element_size()
+        align = max(1, ALIGN_BYTES // esize)
+        target = max(align * self.world_size, grad_bucket_bytes() // esize)
+        by_backward = sorted(range(len(b.params)), key=lambda k: b.order[k], reverse=True)
+        b.subs, b.sub_of, b.goffset = [], [0] * len(b.params), [0] * len(b.params)
+        pieces, fill, members = [], [0] * self.world_size, []
+        for k in by_backward:
+            members.append((k, fill[b.owner[k]]))
+            fill[b.owner[k]] += (b.params[k].numel() + align - 1) // align * align
+            if max(fill) * self.world_size >= target:
+                pieces.append((members, max(fill)))
+                fill, members = [0] * self.world_size, []
+        if members:
+            pieces.append((members, max(fill)))
+        start = 0
+        for members, part in pieces:
+            part = max(part, align)
+            sub = SubBucket(start, part)
+            for k, rel in members:
+                b.sub_of[k] = len(b.subs)
+                b.goffset[k] = start + b.owner[k] * part + rel
+            b.subs.append(sub)
+            start += part * self.world_size
+        return max(start, align)
+
     def attach_grad_buffers(self, fused_pull: bool = False) -> None:
         """Allocate the flat gradient buffers and make every ``p.grad`` a view so that autograd
         accumulates straight into them.  With ``fused_pull`` (and a peer-mapped parameter buffer)
@@ -199,7 +264,7 @@ class ShardPlan:
         for b in self.buckets.values():
             if b.gflat is not None:
                 continue
-            n = b.segment * self.world_size
+            n = self._layout_grad_pieces(b)
             if fused_pull and b.peer_ptrs is not None:
                 import torch.distributed._symmetric_memory as symm
                 b.gflat = symm.empty(n, dtype=b.dtype, device=b.device)
@@ -212,12 +277,14 @@ class ShardPlan:
                 b.gflat = torch.zeros(n, dtype=b.dtype, device=b.device)
             b.grad_views = []
             b.expected = 0
-            for p, off in zip(b.params, b.offset):
+            for k, p in enumerate(b.params):
                 if p.requires_grad:
+                    off = b.goffset[k]
                     view = b.gflat[off:off + p.numel()].view(p.shape)
                     b.grad_views.append(view)
                     p.grad = view
                     b.expected += 1
+                    b.subs[b.sub_of[k]].expected += 1
                 else:
                     b.grad_views.append(None)
 

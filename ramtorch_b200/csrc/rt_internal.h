@@ -28,8 +28,6 @@ constexpr uint32_t kVecOk = 1u;  // all four pointers are 16-byte aligned
 constexpr int kChunkShiftBit = 8;  // flags bits 8..11: a CTA covers (kPieceElems << shift) elements
 constexpr int64_t kBigLaunchChunks = 65536;       // launches of at least this many 8192-element chunks ...
 constexpr int64_t kLongTensorElems = 1 << 20;     // ... give tensors at least this long the longer CTAs
-constexpr int64_t kSmallLaunchElems = (int64_t)1 << 25;  // launches below this get short CTAs
-constexpr int kSmallShift = 1;                    // ... of (kPieceElems << kSmallShift) elements
 
 // Peer copies of a shared parameter region (kernel argument; n == 0 disables).
 struct PushTable {
@@ -92,7 +90,6 @@ int launch_adamw(int pd, int gd, int sd, const DevTensor* table, const uint2* ch
                  const PeerTables* peers, const HyperPack* pack);
 int check_launchable(int pd, int gd, int sd, uint32_t flags, const PeerTables* peers);
 int cta_shift(int64_t launch_elems, int64_t tensor_elems, bool all16);
-int small_shift();
 int64_t set_cta_shift(DevTensor& t, int64_t launch_elems, int pd, int gd, int sd);
 int launch_adamw_debug(int pd, int gd, int sd, const DevTensor& one, const rt_hyper& one_h,
                        uint64_t seed, const rt_debug& dbg, cudaStream_t stream);

@@ -14,9 +14,7 @@ import torch
 import torch.distributed as dist
 
 from ._native import trace as _trace
-from ._shard_plan import ALIGN_BYTES, ShardPlan, plan_for
-
-PARAM_IDS_KEY = "rt_param_ids"
+from ._shard_plan import ALIGN_BYTES, PARAM_IDS_KEY, ShardPlan, plan_for
 
 
 class ZeroParamGroups(dict):

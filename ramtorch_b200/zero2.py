@@ -3,10 +3,12 @@
 The reference registers, on every parameter of every rank's groups, a hook that issues
 ``dist.reduce(grad, dst=owner, SUM)`` per tensor per backward (ramtorch/zero2.py:27-57).  The
 contract a training loop relies on is: after ``backward``, the owner's gradient of each parameter
-it owns is the SUM over ranks.  Here that is delivered by ONE in-place NCCL ``reduce_scatter``
-per (device, dtype) over a flat gradient buffer laid out like the ZeRO-1 parameter buffer:
-``p.grad`` of every parameter is a view into it, autograd accumulates in place, and the
-reduce-scatter is launched by the hook of the last gradient to arrive.
+it owns is the SUM over ranks.  Here that is delivered by in-place NCCL ``reduce_scatter``s over a
+flat gradient buffer per (device, dtype): ``p.grad`` of every parameter is a view into it and
+autograd accumulates in place.  The buffer is cut into pieces of about 256 MiB in the order in
+which backward completes them; the hook of the last gradient of a piece launches that piece's
+reduce-scatter at once, so the reduction overlaps the rest of backward (as the reference's
+per-tensor reduce does) while still moving a few large messages instead of one per tensor.
 
 CPU-resident ``is_ramtorch`` parameters keep the reference's hook-dict protocol under the name
 ``_ramtorch_zero_2_hooks`` (zero2.py:67-72) with its synchronous per-tensor reduce, because their
@@ -27,27 +29,72 @@ from .helpers import ZERO2_HOOK_NAME, register_ramtorch_hook
 _ACTIVE_PLANS = weakref.WeakSet()
 
 
-def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int) -> None:
-    """Sum the flat gradient buffer across ranks into each owner's segment, then clear the
-    segments this rank does not own so that a later micro-batch accumulates onto zeros there
-    (which keeps gradient accumulation equal to the reference's reduce-every-backward)."""
+def _launch_piece(plan: ShardPlan, bucket: Bucket, sub, rank: int) -> None:
+    """Start the reduce-scatter of one complete piece of the flat gradient buffer.  NCCL runs it on
+    its own stream, ordered after what the current stream has written so far, so the rest of
+    backward overlaps it; nothing waits here."""
+    sub.ready = 0
+    region = bucket.gflat[sub.start:sub.start + sub.part * plan.world_size]
+    mine = region[rank * sub.part:(rank + 1) * sub.part]
+    with _trace("rt.zero2.reduce_scatter"):
+        sub.work = dist.reduce_scatter_tensor(mine, region, op=dist.ReduceOp.SUM, async_op=True)
+    # The parts this rank does not own are cleared again, so that a later micro-batch accumulates
+    # onto zeros there (which keeps gradient accumulation equal to the reference's
+    # reduce-every-backward).  That pass runs on a side stream behind the collective, off the
+    # critical path; only _finish_pieces makes anyone wait for it.
+    if bucket.side is None:
+        bucket.side = torch.cuda.Stream(bucket.device) if bucket.device.type == "cuda" else False
+    if bucket.side:
+        with torch.cuda.stream(bucket.side):
+            sub.work.wait()
+            _clear_others(region, sub.part, rank)
+            sub.zeroed = torch.cuda.Event()
+            sub.zeroed.record()
+            region.record_stream(bucket.side)
+    else:                                   # CPU tensors (gloo): no streams, the collective has to finish first
+        sub.work.wait()
+        sub.work = None
+        _clear_others(region, sub.part, rank)
+
+
+def _clear_others(region: torch.Tensor, part: int, rank: int) -> None:
+    region[:rank * part].zero_()
+    region[(rank + 1) * part:].zero_()
+
+
+def _finish_pieces(bucket: Bucket) -> None:
+    """Order the current stream after every reduce-scatter (and clearing pass) started so far."""
+    for sub in bucket.subs:
+        if sub.work is not None:
+            sub.work.wait()       # stream-level wait; the host does not block on NCCL
+            sub.work = None
+        if sub.zeroed is not None:
+            torch.cuda.current_stream(bucket.device).wait_event(sub.zeroed)
+            sub.zeroed = None
+
+
+def _reduce_bucket(plan: ShardPlan, bucket: Bucket, rank: int, only_started: bool = False) -> None:
+    """Sum the flat gradient buffer across ranks into each owner's parts: every piece that has not
+    been reduced since its gradients arrived is reduced now, then the current stream is ordered
+    after all of them.  ``only_started``: reduce only pieces that received at least one gradient."""
     bucket.ready = 0
     written, bucket.grads_written = bucket.grads_written, False
     if plan.world_size == 1 or not dist.is_initialized():
+        for sub in bucket.subs:
+            sub.ready = 0
         return
     if bucket.gpeer_ptrs is not None:
         # fused reduction: the optimizer kernel will read every rank's copy itself; all that is
         # needed here is that no rank starts reading before every rank has finished writing
+        for sub in bucket.subs:
+            sub.ready = 0
         if written:
             dist.all_reduce(_barrier_token(bucket))
         return
-    with _trace("rt.zero2.reduce_scatter"):
-        mine = bucket.rank_segment(bucket.gflat, rank)
-        work = dist.reduce_scatter_tensor(mine, bucket.gflat, op=dist.ReduceOp.SUM, async_op=True)
-        work.wait()   # orders the current stream after the collective; the host does not block on NCCL
-        lo, hi = rank * bucket.segment, (rank + 1) * bucket.segment
-        bucket.gflat[:lo].zero_()
-        bucket.gflat[hi:].zero_()
+    for sub in bucket.subs:
+        if sub.work is None and (sub.ready > 0 or not only_started):
+            _launch_piece(plan, bucket, sub, rank)
+    _finish_pieces(bucket)
 
 
 def _barrier_token(bucket: Bucket) -> torch.Tensor:
@@ -63,9 +110,15 @@ def finish_grad_sync() -> None:
     times, as with any collective."""
     for plan in list(_ACTIVE_PLANS):
         for bucket in plan.buckets.values():
-            if bucket.gflat is not None and (bucket.ready > 0 or
-                                             (bucket.gpeer_ptrs is not None and bucket.grads_written)):
+            if bucket.gflat is None:
+                continue
+            pending = any(sub.work is not None or sub.zeroed is not None for sub in bucket.subs)
+            if bucket.ready > 0 or (bucket.gpeer_ptrs is not None and bucket.grads_written):
+                # a partial backward (unused parameters): every rank reduces every piece, so that the
+                # collectives stay matched whatever each rank's autograd graph touched
                 _reduce_bucket(plan, bucket, plan.current_rank)
+            elif pending:
+                _finish_pieces(bucket)
 
 
 def reduce_gradients_now(rank_param_groups) -> None:
@@ -106,6 +159,7 @@ def setup_grad_sharding_hooks(rank_param_groups, current_rank):
 
     def make_flat_hook(bucket: Bucket, index: int):
         view = bucket.grad_views[index]
+        sub = bucket.subs[bucket.sub_of[index]]
 
         def hook(param):
             grad = param.grad
@@ -116,12 +170,21 @@ def setup_grad_sharding_hooks(rank_param_groups, current_rank):
                     view.copy_(grad)
                 param.grad = view
             bucket.ready += 1
+            sub.ready += 1
             bucket.grads_written = True
+            fused = bucket.gpeer_ptrs is not None
+            distributed = plan.world_size > 1 and dist.is_initialized()
+            if not fused and distributed and sub.ready >= sub.expected and sub.work is None:
+                _launch_piece(plan, bucket, sub, current_rank)     # overlaps the rest of backward
             if bucket.ready >= bucket.expected:
-                if bucket.gpeer_ptrs is not None:
-                    bucket.ready = 0          # fused reduction: the barrier waits for optimizer.step()
+                bucket.ready = 0
+                if fused or not distributed:
+                    for piece in bucket.subs:
+                        piece.ready = 0   # fused reduction: the barrier waits for optimizer.step()
                 else:
-                    _reduce_bucket(plan, bucket, current_rank)
+                    # backward is over for this bucket: launch what a repeated parameter may have
+                    # left behind and order the current stream after all pieces
+                    _reduce_bucket(plan, bucket, current_rank, only_started=True)
 
         return hook
 

@@ -245,6 +245,67 @@ def test_stochastic_rounding_is_unbiased_over_a_million_trials():
         assert abs(o.mean() - float(x32)) <= 3 * sigma + 1e-30
 
 
+def test_shared_draws_stay_unbiased_and_couple_only_the_documented_lanes():
+    """RT_HYPER_SHARED_DRAWS (the optimizer class's default): one Philox block serves p, ema and
+    ema_squared of a group of eight, ema reading two lanes further and ema_squared four.  Over 2^20
+    elements with identical inputs: each of the three roundings is unbiased within 3 sigma; the
+    three roundings OF ONE ELEMENT are uncorrelated; and the pairs that do share a draw -- p[i] with
+    ema[i-2] and ema_squared[i-4] inside a group -- are coupled exactly as much as two thresholds on
+    one uniform number are: corr = (min(fa, fb) - fa fb) / sqrt(fa (1 - fa) fb (1 - fb))."""
+    from ramtorch_b200 import _native as N
+    n, step = 1 << 20, 100
+    dev = torch.device("cuda")
+    const = dict(p=0.0123, g=7.3e-4, m=-4.1e-4, v=3.3e-7)
+    bits16 = {k: oracle.f32_to_bf16_bits_rn(np.full(n, x, np.float32)) for k, x in const.items()}
+    hn = N.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, step, shared_draws=True)
+    ho = oracle.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, step, shared_draws=True)
+    tp, tg, tm, tv = (to_torch(bits16[k], "bf16", dev) for k in "pgmv")
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, seed=2024, tensor_id=3)
+    torch.cuda.synchronize()
+    small = {k: bits16[k][:8].copy() for k in "pgmv"}
+    f32 = oracle.adamw_sr(small["p"], small["g"], small["m"], small["v"], oracle.BF16, oracle.BF16, oracle.BF16, ho,
+                          seed=2024, tensor_id=3, want_f32=True)
+    floor16, frac = {}, {}
+    for name, x in zip("pmv", f32):
+        b = int(np.array([x[0]], np.float32).view(np.uint32)[0])
+        floor16[name], frac[name] = b >> 16, (b & 0xFFFF) / 65536.0
+        assert 0.05 < frac[name] < 0.95                       # a fraction worth testing
+
+    def round_ups(tensors):
+        """1.0 where an element was rounded up; also checks floor/ceil and the mean (3 sigma)."""
+        up = {}
+        for name, t in zip("pmv", tensors):
+            out = to_numpy(t).astype(np.int64)
+            assert set(np.unique(out)) <= {floor16[name], floor16[name] + 1}   # floor or ceil of the fp32 value
+            up[name] = (out != floor16[name]).astype(np.float64)
+            sigma = np.sqrt(frac[name] * (1 - frac[name]) / n)
+            assert abs(up[name].mean() - frac[name]) <= 3 * sigma, name
+        return up
+
+    def corr(a, b):
+        return float(np.corrcoef(a, b)[0, 1])
+
+    def shifted(x, lanes):        # x[i] <- x[(i - lanes) within its group of eight]
+        return x.reshape(-1, 8)[:, (np.arange(8) - lanes) % 8].ravel()
+
+    noise = 4.0 / np.sqrt(n)
+    up = round_ups((tp, tm, tv))
+    # same element, different tensors: different draws
+    assert abs(corr(up["p"], up["m"])) <= noise and abs(corr(up["p"], up["v"])) <= noise and abs(corr(up["m"], up["v"])) <= noise
+    # the coupled pairs
+    for other, lanes in (("m", 2), ("v", 4)):
+        fa, fb = frac["p"], frac[other]
+        want = (min(fa, fb) - fa * fb) / np.sqrt(fa * (1 - fa) * fb * (1 - fb))
+        assert abs(corr(up["p"], shifted(up[other], lanes)) - want) <= noise, other
+    # with independent blocks (flags = 0) the same pairs are uncorrelated
+    hn.flags = 0
+    tp, tg, tm, tv = (to_torch(bits16[k], "bf16", dev) for k in "pgmv")
+    F.adamw_sr_flat_(tp, tg, tm, tv, hn, seed=2024, tensor_id=3)
+    torch.cuda.synchronize()
+    ind = round_ups((tp, tm, tv))
+    assert abs(corr(ind["p"], shifted(ind["m"], 2))) <= noise and abs(corr(ind["p"], shifted(ind["v"], 4))) <= noise
+
+
 def test_large_flat_tensor_spot_checked_against_checker():
     """2^27 elements (fp32 moments, the roofline configuration's dtypes): whole-buffer
     properties plus slices recomputed by the checker at their own index0."""

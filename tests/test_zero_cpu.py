@@ -100,13 +100,22 @@ def _worker(rank, world, port, scenario, out):
 
 
 def _spawn(scenario, world):
+    import queue
     ctx = mp.get_context("spawn")
-    out = ctx.SimpleQueue()
+    out = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, world, port, scenario, out)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [out.get() for _ in procs]
+    results = []
+    try:
+        for _ in procs:
+            results.append(out.get(timeout=180))      # a worker that died must not hang the test
+    except queue.Empty:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        pytest.fail(f"only {len(results)} of {world} workers reported (exit codes {[p.exitcode for p in procs]})")
     for p in procs:
         p.join(timeout=60)
     return sorted(results)
@@ -150,6 +159,42 @@ def _scenario_full_loop(rank, world):
             model.zero_grad(set_to_none=False)
         ref.zero_grad()
     return True
+
+
+def _scenario_small_pieces(rank, world):
+    """The same loop with gradient pieces of 256 bytes: several reduce-scatters per backward, launched
+    as their pieces complete, with a partial backward (unused head) in between."""
+    os.environ["RT_ZERO2_BUCKET_MB"] = str(256 / (1 << 20))
+    try:
+        from ramtorch_b200._shard_plan import plan_for as _pf
+        ok = _scenario_full_loop(rank, world)
+        # and the layout really was cut up: rebuild the plan of an equal model to look at it
+        model = _model()
+        rpg = create_zero_param_groups([{"params": list(model.parameters())}], world)
+        setup_grad_sharding_hooks(rpg, rank)
+        (bucket,) = _pf(rpg).buckets.values()
+        pieces = len(bucket.subs)
+        covered = sorted((bucket.goffset[k], bucket.goffset[k] + p.numel()) for k, p in enumerate(bucket.params))
+        disjoint = all(a[1] <= b[0] for a, b in zip(covered, covered[1:]))
+        for p in model.parameters():
+            assert p.grad.data_ptr() == bucket.gflat.data_ptr() + 4 * bucket.goffset[[id(q) for q in bucket.params].index(id(p))]
+        # a backward that leaves the last layer out: step time reduces every piece on every rank
+        from ramtorch_b200.zero2 import finish_grad_sync
+        x = torch.randn(4, 13, generator=torch.Generator().manual_seed(rank))
+        model[:3](x).square().sum().backward()
+        finish_grad_sync()
+        first = model[0].weight
+        mine = any(first is q for g in rpg[rank] for q in g["params"])
+        total = torch.zeros_like(first)
+        for r in range(world):
+            ref = _model()
+            xr = torch.randn(4, 13, generator=torch.Generator().manual_seed(r))
+            ref[:3](xr).square().sum().backward()
+            total += ref[0].weight.grad
+        partial_ok = (not mine) or torch.allclose(first.grad, total, rtol=1e-5, atol=1e-6)
+        return True if (ok and pieces >= 3 and disjoint and partial_ok) else (ok, pieces, disjoint, partial_ok)
+    finally:
+        os.environ.pop("RT_ZERO2_BUCKET_MB", None)
 
 
 def _scenario_plan_mismatch(rank, world):
@@ -199,11 +244,11 @@ def _scenario_rank_leaves(rank, world):
 
 
 SCENARIOS = {"rank_leaves": _scenario_rank_leaves, "full_loop": _scenario_full_loop, "plan_mismatch": _scenario_plan_mismatch,
-             "ramtorch_hooks": _scenario_ramtorch_hooks}
+             "ramtorch_hooks": _scenario_ramtorch_hooks, "small_pieces": _scenario_small_pieces}
 
 
-@pytest.mark.parametrize("scenario,world", [("full_loop", 2), ("full_loop", 3), ("plan_mismatch", 2),
-                                            ("ramtorch_hooks", 2), ("rank_leaves", 2)])
+@pytest.mark.parametrize("scenario,world", [("full_loop", 2), ("full_loop", 3), ("small_pieces", 2), ("small_pieces", 3),
+                                            ("plan_mismatch", 2), ("ramtorch_hooks", 2), ("rank_leaves", 2)])
 def test_gloo_ranks(scenario, world):
     results = _spawn(scenario, world)
     assert len(results) == world

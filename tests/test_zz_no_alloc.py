@@ -73,6 +73,57 @@ def test_static_entry_point_matches_the_plan_entry_point_on_two_consecutive_step
         lib.rt_plan_destroy(plan)
 
 
+def _np_bits(t):
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16).ravel().copy()
+    return t.numpy().ravel().copy()
+
+
+@pytest.mark.gpu
+def test_static_entry_point_against_the_cpu_checker_and_without_touching_the_allocator():
+    """The same call checked on its own terms: its output equals the CPU checker's bit for bit
+    (ragged sizes with scalar tails, three dtype combinations, six hyper rows -- more than ride
+    along as kernel arguments on the plan path), a second call with a different, shorter tensor
+    list reuses the shared tables correctly, and neither call changes what the CUDA allocator or
+    PyTorch's caching allocator hold."""
+    import oracle
+    lib = N.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = N.stream_ptr(dev)
+    code = {torch.bfloat16: oracle.BF16, torch.float32: oracle.F32}
+
+    def run(tensors, step, seed):
+        rows = [dict(HP, lr=1e-4 * (k + 1), weight_decay=0.01 * (k % 2)) for k in range(6)]
+        hyper = (N.Hyper * 6)(*[N.make_hyper(step=step, **r) for r in rows])
+        descs = _descs(tensors)
+        for k in range(len(tensors)):
+            descs[k].hyper_index = k % 6
+        want = []
+        for k, (p, g, m, v) in enumerate(tensors):       # the checker's answer, before the GPU overwrites the inputs
+            hp, hg, hm, hv = (_np_bits(t) for t in (p, g, m, v))
+            oracle.adamw_sr(hp, hg, hm, hv, code[p.dtype], code[g.dtype], code[m.dtype],
+                            oracle.make_hyper(step=step, **rows[k % 6]), seed=seed, tensor_id=100 + k)
+            want.append((hp, hm, hv))
+        torch.cuda.synchronize()
+        free0, alloc0, reserved0 = torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)
+        N.check(lib.rt_adamw_sr_multi_static(descs, len(tensors), hyper, 6, seed, stream), "rt_adamw_sr_multi_static")
+        torch.cuda.synchronize()
+        after = (torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+        for (p, _, m, v), (wp, wm, wv) in zip(tensors, want):
+            assert np.array_equal(_np_bits(p), wp) and np.array_equal(_np_bits(m), wm) and np.array_equal(_np_bits(v), wv)
+        return (free0, alloc0, reserved0), after
+
+    first = _make(dev, 11)
+    run(first, 3, 1234)                 # warm-up call: looks up the array's address, loads the kernels' code
+    before, after = run(first, 4, 1234)
+    assert before == after              # nothing allocated or freed by the call, by anyone
+    shorter = _make(dev, 12)[1:4]       # a different, shorter list right behind it on the same stream
+    before, after = run(shorter, 9, 77)
+    assert before == after
+
+
 def test_static_entry_point_rejects_requests_beyond_its_fixed_tables():
     """Host-side checks only: nothing is launched, so this part needs no GPU."""
     lib = N.lib()
@@ -89,3 +140,12 @@ def test_static_entry_point_rejects_requests_beyond_its_fixed_tables():
     assert b"65536 chunks" in lib.rt_last_error()
     assert lib.rt_adamw_sr_multi_static(one, 1, h, 65, 0, None) == -3
     assert lib.rt_adamw_sr_multi_static(one, 0, h, 1, 0, None) == 0
+    # a hyper row that asks for centralization needs the tensor's row means, as on the plan path
+    one[0].numel = 64
+    c = (N.Hyper * 1)(N.make_hyper(step=1, centralization=0.5, **HP))
+    assert lib.rt_adamw_sr_multi_static(one, 1, c, 1, 0, None) == -6
+    assert b"row_mean" in lib.rt_last_error()
+    # flag bits the library does not know are refused, not ignored
+    bad = (N.Hyper * 1)(N.make_hyper(step=1, **HP))
+    bad[0].flags = 1
+    assert lib.rt_adamw_sr_multi_static(one, 1, bad, 1, 0, None) == -6
