@@ -382,7 +382,7 @@ def zero_parity_check(rank, world, device):
                     p.grad = None
             torch.cuda.synchronize()
             used = sorted({str(b.mode) for b in plan_for(rpg).buckets.values()})
-            flat = torch.cat([p.detach().reshape(-1).view(torch.int16) for p in params])
+            flat = torch.cat([p.detach().reshape(-1) for p in params])     # bf16: a type NCCL can move
             everyone = [torch.empty_like(flat) for _ in range(world)] if rank == 0 else None
             dist.gather(flat, everyone, dst=0)
             bad = 0
@@ -436,7 +436,7 @@ def _parity_against_checker(start, groups, params, everyone, world, np):
     want = np.concatenate(want)
     bad = 0
     for copy in everyone:
-        got = copy.cpu().numpy().view(np.uint16)
+        got = copy.cpu().view(torch.int16).numpy().view(np.uint16)
         bad += int((got != want).sum())
     return bad
 

@@ -229,9 +229,14 @@ class ShardPlan:
 
     def _layout_grad_pieces(self, b: Bucket) -> int:
         """Cut the bucket's gradients into sub-buckets.  Parameters are taken in reverse registration
-        order (the order in which backward finishes them) and a piece is closed once it holds the
-        target number of bytes; inside a piece each rank's tensors are packed into that rank's part.
-        Returns the length of the flat gradient buffer in elements."""
+        order (the order in which backward finishes them); inside a piece each rank's tensors are
+        packed into that rank's part, and all parts of a piece are as long as its longest.  A piece
+        is closed once it holds the target number of bytes AND its parts are balanced (padding
+        below 1/8 of the piece): a piece closed right after one huge tensor would consist
+        mostly of the other ranks' empty parts, which the reduce-scatter would still move.  A
+        lopsided last piece is merged into the one before it, and an ownership that never
+        balances ends up as one piece, i.e. one collective at the end of backward.  Returns the
+        length of the flat gradient buffer in elements."""
         esize = torch.empty((), dtype=b.dtype).element_size()
         align = max(1, ALIGN_BYTES // esize)
         target = max(align * self.world_size, grad_bucket_bytes() // esize)
@@ -241,14 +246,20 @@ class ShardPlan:
         for k in by_backward:
             members.append((k, fill[b.owner[k]]))
             fill[b.owner[k]] += (b.params[k].numel() + align - 1) // align * align
-            if max(fill) * self.world_size >= target:
-                pieces.append((members, max(fill)))
+            span, useful = max(fill) * self.world_size, sum(fill)
+            if useful >= target and (span - useful) * 8 < span:
+                pieces.append((members, list(fill)))
                 fill, members = [0] * self.world_size, []
         if members:
-            pieces.append((members, max(fill)))
+            if pieces and (max(fill) * self.world_size - sum(fill)) * 4 > max(fill) * self.world_size:
+                # the tail is more than a quarter padding: append it to the previous piece
+                prev_members, prev_fill = pieces.pop()
+                members = prev_members + [(k, rel + prev_fill[b.owner[k]]) for k, rel in members]
+                fill = [a + c for a, c in zip(prev_fill, fill)]
+            pieces.append((members, list(fill)))
         start = 0
-        for members, part in pieces:
-            part = max(part, align)
+        for members, fills in pieces:
+            part = max(max(fills), align)
             sub = SubBucket(start, part)
             for k, rel in members:
                 b.sub_of[k] = len(b.subs)

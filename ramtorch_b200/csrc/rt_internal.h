@@ -34,7 +34,6 @@ struct PushTable {
   const char* local;          // base of the region in this GPU's memory
   int64_t bytes;
   int n;                      // number of peers
-  int order;                  // 0: peer stores after the local store, 1: before it
   char* base[RT_MAX_PEERS];   // the region's base in each peer's memory, as mapped here
 };
 
@@ -64,7 +63,7 @@ struct PullTable {
   int64_t bytes;
   int n;                      // number of ranks
   int self;                   // this rank's index (its copy is read from t.g directly)
-  int staged;                 // set by the launcher: peers' words are staged through shared memory
+  int staged;                 // set by the launcher: 0, or the number of shared-memory slots (2..4) the peers' words are staged through
   const char* base[RT_MAX_PEERS + 1];
 };
 
