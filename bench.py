@@ -179,7 +179,8 @@ def cpu_baseline(steps=3, warmup=1, sample_elems=None):
         list(ex.map(fill, range(0, n, blk)))
     times = []
     for k in range(warmup + steps):
-        h = oracle.make_hyper(HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"], START_STEP + 1 + k)
+        h = oracle.make_hyper(HP["lr"], HP["betas"], HP["eps"], HP["weight_decay"], START_STEP + 1 + k,
+                              reference_order=True)     # the reference's own operation order
         t0 = time.perf_counter()
         oracle.adamw_sr(p, g, m, v, oracle.BF16, oracle.BF16, oracle.F32, h, seed=0, tensor_id=0)
         dt = time.perf_counter() - t0
@@ -246,10 +247,13 @@ WORKLOADS = {
 }
 
 
-def link_ceiling(device, nbytes=1 << 30, reps=4, world=1):
-    """Pinned cudaMemcpyAsync rates of this box: each direction alone and both at once (GB/s).  With
-    world > 1 every rank measures at the same time (between barriers), which is what the ranks of a
-    streamed step get: they share the host's memory and PCIe root complexes."""
+def link_ceiling(device, nbytes=1 << 30, reps=4, world=1, mix=(1, 1)):
+    """Pinned cudaMemcpyAsync rates of this box: each direction alone, both at once with equal
+    bytes, and both at once with the workload's own byte ratio `mix` = (bytes in, bytes out) --
+    the time of that last run is what a perfect pipeline of the streamed step would need, so its
+    total rate (`mix_total_gbs`) is the ceiling the step is held against.  With world > 1 every
+    rank measures at the same time (between barriers), which is what the ranks of a streamed step
+    get: they share the host's memory and PCIe root complexes."""
     import torch
     import torch.distributed as dist
     h_in = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
@@ -258,7 +262,7 @@ def link_ceiling(device, nbytes=1 << 30, reps=4, world=1):
     d_out = torch.empty(nbytes, dtype=torch.uint8, device=device)
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
-    def run(h2d, d2h, n):
+    def run(h2d, d2h, n, n_in=nbytes, n_out=nbytes):
         torch.cuda.synchronize(device)
         if world > 1:
             dist.barrier()
@@ -266,24 +270,35 @@ def link_ceiling(device, nbytes=1 << 30, reps=4, world=1):
         for _ in range(n):
             if h2d:
                 with torch.cuda.stream(s_in):
-                    d_in.copy_(h_in, non_blocking=True)
+                    d_in[:n_in].copy_(h_in[:n_in], non_blocking=True)
             if d2h:
                 with torch.cuda.stream(s_out):
-                    h_out.copy_(d_out, non_blocking=True)
+                    h_out[:n_out].copy_(d_out[:n_out], non_blocking=True)
         torch.cuda.synchronize(device)
-        return nbytes * n / (time.perf_counter() - t0) / 1e9
+        dt = time.perf_counter() - t0
+        return ((n_in if h2d else 0) + (n_out if d2h else 0)) * n / dt / 1e9
 
     run(True, True, 1)
+    big = max(mix)
+    n_in, n_out = (int(nbytes * mix[0] / big) // 256 * 256, int(nbytes * mix[1] / big) // 256 * 256)
     out = {"h2d_alone_gbs": run(True, False, reps), "d2h_alone_gbs": run(False, True, reps),
-           "both_each_gbs": run(True, True, reps), "ranks_measuring_at_once": world}
+           "both_each_gbs": run(True, True, reps) / 2, "mix_total_gbs": run(True, True, reps, n_in, n_out),
+           "mix": list(mix), "ranks_measuring_at_once": world}
     if world > 1:
-        t = torch.tensor([out["h2d_alone_gbs"], out["d2h_alone_gbs"], out["both_each_gbs"]], device=device,
-                         dtype=torch.float64)
+        keys = ("h2d_alone_gbs", "d2h_alone_gbs", "both_each_gbs", "mix_total_gbs")
+        t = torch.tensor([out[k] for k in keys], device=device, dtype=torch.float64)
         lo = t.clone(); dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        out["min_over_ranks"] = dict(zip(("h2d_alone_gbs", "d2h_alone_gbs", "both_each_gbs"), lo.tolist()))
-        out["sum_over_ranks"] = dict(zip(("h2d_alone_gbs", "d2h_alone_gbs", "both_each_gbs"), t.tolist()))
+        out["min_over_ranks"] = dict(zip(keys, lo.tolist()))
+        out["sum_over_ranks"] = dict(zip(keys, t.tolist()))
     return out
+
+
+def link_frac(h2d_gbs, d2h_gbs, ceiling, world):
+    """Achieved host-link traffic (both directions) over what concurrent pinned copies with the same
+    byte ratio reach in the same run (slowest rank when several measure at once)."""
+    top = ceiling["min_over_ranks"]["mix_total_gbs"] if world > 1 else ceiling["mix_total_gbs"]
+    return (h2d_gbs + d2h_gbs) / top, top
 
 
 def nvlink_ceiling(device, rank, world, chunk_bytes=64 << 20, reps=8):
@@ -543,22 +558,34 @@ def measure_resident(wl, args, device, rank, world, *, steps, warmup, independen
     fence()
     sampler = ClockSampler(local) if rank == 0 else None
     rs_events.clear()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1)]
+    # Per-step events split a step into update and redistribution.  On one GPU there is nothing to
+    # split, and for steps of tens of microseconds the two event records per step would themselves
+    # be a tenth of what is measured: such loops are bracketed by one pair of events only.
+    per_step = world > 1 or steps <= 64
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps + 1 if per_step else 2)]
     launches0 = N.stats()["kernel_launches"]
     t_wall0 = time.time()
     ev[0].record()
-    for k in range(steps):
-        one_step(k)
-        ev[2 * k + 1].record()
-        redistribute(k)
-        ev[2 * k + 2].record()
+    if per_step:
+        for k in range(steps):
+            one_step(k)
+            ev[2 * k + 1].record()
+            redistribute(k)
+            ev[2 * k + 2].record()
+    else:
+        for k in range(steps):
+            steppers[k % len(steppers)].step()
+        ev[1].record()
     host_ms = (time.time() - t_wall0) * 1e3 / steps
     fence()
     t_wall1 = time.time()
     launches = N.stats()["kernel_launches"] - launches0
-    total_ms = ev[0].elapsed_time(ev[2 * steps])
-    upd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
-    ag_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
+    total_ms = ev[0].elapsed_time(ev[-1])
+    if per_step:
+        upd_ms = sum(ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(steps)) / steps
+        ag_ms = sum(ev[2 * k + 1].elapsed_time(ev[2 * k + 2]) for k in range(steps)) / steps
+    else:
+        upd_ms, ag_ms = total_ms / steps, 0.0
     clocks = sampler.window(t_wall0, t_wall1) if sampler else None
     sync_ms = None
     if grad_sync and len(rs_events) == steps:
@@ -743,14 +770,14 @@ def measure_c4(args, device, rank, world, steps=3, chunk_elems=1 << 27, ring_dep
     del opt, params
     gc.collect()
     torch.cuda.empty_cache()
-    ceiling = link_ceiling(device, world=world)
     h2d = (s1["h2d_bytes"] - s0["h2d_bytes"]) / steps
     d2h = (s1["d2h_bytes"] - s0["d2h_bytes"]) / steps
+    ceiling = link_ceiling(device, world=world, mix=(int(h2d), int(d2h)))
     total = int(elems.item())
-    both = ceiling["min_over_ranks"]["both_each_gbs"] if world > 1 else ceiling["both_each_gbs"]
     link = {"h2d_gbs_per_gpu": h2d / (ms * 1e-3) / 1e9, "d2h_gbs_per_gpu": d2h / (ms * 1e-3) / 1e9,
             "ceiling": ceiling, "pcie_gen5_x16_nominal_gbs_per_direction": 63.0}
-    link["frac_of_measured_bidirectional"] = (link["h2d_gbs_per_gpu"] + link["d2h_gbs_per_gpu"]) / (2 * both)
+    link["frac_of_measured_bidirectional"], link["ceiling_total_gbs"] = link_frac(
+        link["h2d_gbs_per_gpu"], link["d2h_gbs_per_gpu"], ceiling, world)
     return dict(ms=ms, total=total, steps=steps, h2d=h2d, d2h=d2h, link=link, clocks=clocks,
                 launches=int(s1["kernel_launches"] - s0["kernel_launches"]), chunk_elems=chunk_elems,
                 ring_depth=ring_depth, grads_in_hbm=grads_in_hbm)
@@ -764,7 +791,6 @@ def run_c4(args, device, rank, world):
         link = r["link"]
         e2e = {"value": value, "unit": UNIT, "h2d_bytes_per_step": int(r["h2d"]), "d2h_bytes_per_step": int(r["d2h"]),
                "ms_per_step": r["ms"]}
-        both = link["ceiling"]["min_over_ranks"]["both_each_gbs"] if world > 1 else link["ceiling"]["both_each_gbs"]
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": r["steps"], "warmup": 1,
                 "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
@@ -773,9 +799,10 @@ def run_c4(args, device, rank, world):
                            "l2": "streamed chunks of 1 GiB per slot far exceed L2",
                            "parallelism": f"tensors round-robin over {world} ranks" if world > 1 else "single"},
                 "roofline": {"bound": "host link", "achieved": link["h2d_gbs_per_gpu"] + link["d2h_gbs_per_gpu"],
-                             "peak": 2 * both, "unit": "GB/s",
+                             "peak": link["ceiling_total_gbs"], "unit": "GB/s",
                              "frac": link["frac_of_measured_bidirectional"], "traffic": None,
-                             "peak_source": "pinned cudaMemcpyAsync both directions at once, same run, every rank at once"},
+                             "peak_source": "pinned cudaMemcpyAsync in both directions at once with this step's byte ratio, "
+                                            "same run, every rank at once"},
                 "link": link, "e2e": e2e, "cpu_baseline": None, "gpu_launches": r["launches"], "clocks": r["clocks"]}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -837,10 +864,9 @@ def measure_e2e(args, device, rank, world):
     gc.collect()
     torch.cuda.empty_cache()
     # the ceiling every rank gets while all of them copy at once (they share the host)
-    ceil = link_ceiling(device, world=world)
+    ceil = link_ceiling(device, world=world, mix=(int(h2d), int(d2h)))
     e2e["link_ceiling"] = ceil
-    both = ceil["min_over_ranks"]["both_each_gbs"] if world > 1 else ceil["both_each_gbs"]
-    e2e["frac_of_measured_bidirectional_link"] = (e2e["h2d_gbs"] + e2e["d2h_gbs"]) / (2 * both)
+    e2e["frac_of_measured_bidirectional_link"], e2e["link_ceiling_total_gbs"] = link_frac(e2e["h2d_gbs"], e2e["d2h_gbs"], ceil, world)
     return e2e
 
 

@@ -158,7 +158,13 @@ def stats() -> dict:
     return {k: int(getattr(s, k)) for k, _ in Stats._fields_}
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device) -> int:
+    """The current CUDA stream of `device` (index or torch.device) as a raw handle."""
+    if _RAW_STREAM is not None and isinstance(device, int):
+        return _RAW_STREAM(device)      # same value, without building a torch.cuda.Stream object per call
     return torch.cuda.current_stream(device).cuda_stream
 
 

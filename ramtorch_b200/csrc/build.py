@@ -58,5 +58,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+FASTSCAN_SRC = os.path.join(HERE, "fastscan.cpp")
+FASTSCAN_OUT = os.path.join(PKG, "_fastscan.so")
+
+
+def build_fastscan(force: bool = False) -> str:
+    """Build ``ramtorch_b200/_fastscan.so``, the host-side helper that walks long parameter lists in
+    C++ (g++ against the torch headers of the running interpreter).  It only reads tensor pointers
+    and properties; the optimizer works without it, with per-tensor Python passes instead."""
+    if not force and os.path.exists(FASTSCAN_OUT) and os.path.getmtime(FASTSCAN_OUT) >= os.path.getmtime(FASTSCAN_SRC):
+        return FASTSCAN_OUT
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+    gxx = shutil.which("g++")
+    if not gxx:
+        raise RuntimeError("g++ not found: _fastscan.so cannot be built")
+    inc = ce.include_paths() + [sysconfig.get_paths()["include"]]
+    libs = ce.library_paths()
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-DTORCH_EXTENSION_NAME=_fastscan", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    cmd += [f"-I{i}" for i in inc] + [FASTSCAN_SRC, "-o", FASTSCAN_OUT + ".tmp"]
+    cmd += [f"-L{d}" for d in libs] + [f"-Wl,-rpath,{d}" for d in libs] + ["-ltorch_python", "-ltorch", "-ltorch_cpu", "-lc10"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("g++ failed building _fastscan.so")
+    os.replace(FASTSCAN_OUT + ".tmp", FASTSCAN_OUT)
+    return FASTSCAN_OUT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_fastscan(force="--force" in sys.argv))

@@ -42,6 +42,15 @@ import contextlib
 
 from .. import zero2 as _zero2
 
+import os
+
+try:      # host-side helper: walks long parameter lists in C++ (built by ramtorch_b200.csrc.build)
+    from .. import _fastscan as _FS
+    if os.environ.get("RT_NO_FASTSCAN") == "1":
+        _FS = None
+except ImportError:  # pragma: no cover - the helper is optional; the Python passes below do the same
+    _FS = None
+
 _NULL_CTX = contextlib.nullcontext()
 _GET_EMA, _GET_EMA_SQ, _GET_STEP = (operator.itemgetter(k) for k in ("ema", "ema_squared", "step"))
 _PARAM_IDS_KEY = "rt_param_ids"
@@ -259,6 +268,7 @@ class AdamW(Optimizer):
         self._warned_pageable = False
         self._push_marks = []  # peer-mapped buckets the last validated step fully redistributed
         self._fast = None     # cache that lets an unchanged, fully resident step skip re-validation
+        self._cuda_checked = False
         self.last_step_info = {}
 
         # eager state, as adamw.py:84-104; "cpu" (the string) means pinned, and the pinned
@@ -402,8 +412,10 @@ class AdamW(Optimizer):
         loss = None
         if closure is not None:
             loss = closure()
-        if not torch.cuda.is_available():
-            raise RuntimeError("ramtorch_b200.AdamW needs a CUDA device: there is no CPU fallback")
+        if not self._cuda_checked:
+            if not torch.cuda.is_available():
+                raise RuntimeError("ramtorch_b200.AdamW needs a CUDA device: there is no CPU fallback")
+            self._cuda_checked = True
         lib = N.lib()
         self._keepalive.clear()
         if _zero2._ACTIVE_PLANS:
@@ -618,6 +630,25 @@ class AdamW(Optimizer):
             classes=[key for key, _ in classes], n_groups=len(self.param_groups),
             zero_buffers=self._zero_buffer_count(index),
             state_epoch=self.state.epoch, steps=[st["step"] for st in states])
+        if _FS is not None:
+            f, n = self._fast, len(all_params)
+            f["ids_t"] = torch.empty(n, dtype=torch.int64)
+            _FS.param_ids(all_params, f["ids_t"])
+            f["scan_t"] = torch.empty(n, 3, dtype=torch.int64)
+            _FS.scan_params(all_params, f["ids_t"], f["scan_t"])
+            scan = f["scan_t"].numpy()
+            f["scan"] = scan
+            f["mask"] = scan[:, 1] != 0
+            f["p_ptrs_np"] = scan[f["mask"], 0].copy()
+            f["props_np"] = scan[f["mask"], 2].copy()
+            f["ema_ids_t"] = torch.tensor(list(map(id, f["emas"])), dtype=torch.int64)
+            f["ema_sq_ids_t"] = torch.tensor(list(map(id, f["ema_sqs"])), dtype=torch.int64)
+            f["steps_t"] = torch.tensor(f["steps"], dtype=torch.int64)
+            f["gptrs_np"] = np.empty(int(f["mask"].sum()), dtype=np.uint64)
+            # what a gradient must look like: dense, contiguous, of a known dtype, on this device
+            ok = ((f["props_np"] >> 8) & 3) == 1
+            if not bool(ok.all()) or not bool((((f["props_np"] >> 16) & 0xFFFF) == index + 1).all()):
+                self._fast = None
 
     @staticmethod
     def _zero_buffer_count(index):
@@ -631,6 +662,8 @@ class AdamW(Optimizer):
         if getattr(self.state, "epoch", None) != f["state_epoch"]:
             return False    # a state dict was added, replaced or removed since the cache was armed
         all_params = list(chain.from_iterable(g["params"] for g in groups))
+        if _FS is not None and "scan" in f:
+            return self._step_fast_scanned(lib, f, groups, all_params)
         if list(map(id, all_params)) != f["all_ids"]:
             return False
         grads_all = [p.grad for p in all_params]
@@ -678,6 +711,51 @@ class AdamW(Optimizer):
         for bucket in self._push_marks:
             bucket.pushed = True
         self.last_step_info = dict(launches=plan.launches, resident=len(params), streamed=0, fast=True)
+        if self.sync:
+            torch.cuda.current_stream(index).synchronize()
+        return True
+
+    def _step_fast_scanned(self, lib, f, groups, all_params) -> bool:
+        """The same checks as the Python passes of ``_step_fast``, with the per-tensor work done by
+        the C++ helper: identity of every parameter, data pointers, which parameters have a
+        gradient, each gradient's dtype / contiguity / layout / device, identity of the moment
+        tensors and the step counters."""
+        if len(all_params) != len(f["all_ids"]) or _FS.scan_params(all_params, f["ids_t"], f["scan_t"]) >= 0:
+            return False
+        scan, mask = f["scan"], f["mask"]
+        if not np.array_equal(scan[:, 1] != 0, mask):
+            return False
+        if not (np.array_equal(scan[mask, 0], f["p_ptrs_np"]) and np.array_equal(scan[mask, 2], f["props_np"])):
+            return False
+        states = f["states"]
+        if _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], False) >= 0:
+            return False    # a moment tensor was replaced or a counter edited in place
+        plan = self._plans.get(f["index"])
+        if plan is None or len(plan.grad_ptrs) != len(states):
+            return False
+        for g in groups:
+            if g["centralization"] != 0:
+                return False
+        rows = []
+        for gi, step in f["classes"]:
+            g = groups[gi]
+            rows.append(N.make_hyper(g["lr"], g["betas"], g["eps"], g["weight_decay"], step + 1,
+                                     g["centralization"], self.reference_order, self.shared_draws))
+        hyper_arr = (N.Hyper * len(rows))(*rows)
+        gptrs = f["gptrs_np"]
+        gptrs[:] = scan[mask, 1]
+        index = f["index"]
+        with (_NULL_CTX if torch.cuda.current_device() == index else torch.cuda.device(index)):
+            stream = N.stream_ptr(index)
+            N.check(lib.rt_plan_set_grads(plan.handle, gptrs.ctypes.data_as(ctypes.POINTER(N.c_void_p)), stream),
+                    "rt_plan_set_grads")
+            N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(rows), self.seed & (2 ** 64 - 1), stream),
+                    "rt_adamw_sr_multi")
+        f["classes"] = [(gi, step + 1) for gi, step in f["classes"]]
+        _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], True)   # counters += 1
+        for bucket in self._push_marks:
+            bucket.pushed = True
+        self.last_step_info = dict(launches=plan.launches, resident=len(states), streamed=0, fast=True)
         if self.sync:
             torch.cuda.current_stream(index).synchronize()
         return True

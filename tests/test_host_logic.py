@@ -83,3 +83,57 @@ def test_device_gradient_attribute_only_applies_to_cpu_parameters():
     assert _grad_of(p) is p.rt_device_grad
     p.rt_device_grad = None
     assert _grad_of(p) is p.grad
+
+
+def test_reattach_is_ramtorch_flags_marks_the_tensors_of_flagged_modules_only():
+    """helpers.py:229-253: parameters and buffers that directly belong to a module declaring
+    ``is_ramtorch = True`` get the flag back; everything else is left alone."""
+    import copy
+    from ramtorch_b200.helpers import reattach_is_ramtorch_flags
+
+    class Bouncing(torch.nn.Linear):
+        is_ramtorch = True
+
+    model = torch.nn.Sequential(Bouncing(4, 4), torch.nn.LayerNorm(4), torch.nn.Sequential(Bouncing(4, 2, bias=False)))
+    model[0].register_buffer("scale", torch.ones(1))
+    for p in model[0].parameters():
+        p.is_ramtorch = True
+    clone = copy.deepcopy(model)                         # tensor attributes do not survive this (nor torch.save)
+    assert not any(getattr(p, "is_ramtorch", False) for p in clone.parameters())
+    assert reattach_is_ramtorch_flags(clone) is clone
+    flagged = {n for n, p in clone.named_parameters() if getattr(p, "is_ramtorch", False)}
+    assert flagged == {"0.weight", "0.bias", "2.0.weight"}
+    assert getattr(clone[0].scale, "is_ramtorch", False) and not hasattr(clone[1].weight, "is_ramtorch")
+
+
+def test_byte_balanced_ownership_keeps_the_dict_shape_and_evens_out_the_segments():
+    from ramtorch_b200._shard_plan import plan_for
+    from ramtorch_b200.zero1 import create_zero_param_groups
+    sizes = [1000, 8, 8, 8, 900, 8, 8, 8, 1100, 8, 8, 8]          # round-robin by count gives rank 0 every big tensor
+    norms = [torch.zeros(3) for _ in range(2)]
+    params = [torch.zeros(n) for n in sizes]
+    groups = [{"params": norms, "weight_decay": 0.0}, {"params": params, "tag": "w"}]
+    by_count = create_zero_param_groups(groups, 4)
+    by_bytes = create_zero_param_groups(groups, 4, balance="bytes")
+    for rpg in (by_count, by_bytes):
+        assert sorted(rpg) == [0, 1, 2, 3] and all(len(rpg[r]) == 2 for r in rpg)
+        assert all(rpg[r][1]["tag"] == "w" and rpg[r][0]["weight_decay"] == 0.0 for r in rpg)
+        owned = [id(p) for r in rpg for g in rpg[r] for p in g["params"]]
+        assert sorted(owned) == sorted(map(id, norms + params))                    # every tensor exactly once
+        ids = sorted(i for r in rpg for g in rpg[r] for i in g["rt_param_ids"])
+        assert ids == list(range(len(norms) + len(params)))                        # global positions, whatever the owner
+    load = lambda rpg: [sum(p.numel() for g in rpg[r] for p in g["params"]) for r in rpg]
+    assert max(load(by_count)) == 3003 and max(load(by_bytes)) <= 1100 + 16
+    assert plan_for(by_bytes).buckets and max(load(by_bytes)) < max(load(by_count)) / 2
+    # the same position keeps the same id in both assignments: the random bits do not depend on the owner
+    pos = {id(p): i for r in by_count for g in by_count[r] for p, i in zip(g["params"], g["rt_param_ids"])}
+    assert all(pos[id(p)] == i for r in by_bytes for g in by_bytes[r] for p, i in zip(g["params"], g["rt_param_ids"]))
+    with pytest.raises(ValueError):
+        create_zero_param_groups(groups, 4, balance="size")
+
+
+def test_device_gradient_producer_validates_its_arguments():
+    from ramtorch_b200.helpers import accumulate_device_grad
+    p = torch.zeros(4)
+    with pytest.raises(ValueError, match="HBM"):
+        accumulate_device_grad(p, torch.ones(4))

@@ -439,11 +439,18 @@ def test_streamed_centralized_step_is_bit_identical_to_the_resident_one():
         assert bits_equal(a, b) == 0
 
 
-def test_load_state_dict_in_place_after_the_fast_path_is_armed():
+@pytest.mark.parametrize("helper", ["c++ list scan", "python passes"])
+def test_load_state_dict_in_place_after_the_fast_path_is_armed(helper, monkeypatch):
     """Two steps arm the repeat-step cache; load_state_dict() then swaps every state dict and tensor.
-    The following steps must use the loaded moments and counters, not the cached ones."""
+    The following steps must use the loaded moments and counters, not the cached ones.  Run with
+    the C++ helper that walks the parameter list and with the Python passes it replaces."""
     import copy
     from ramtorch_b200 import AdamW
+    from ramtorch_b200.stochastic_optimizers import adamw as adamw_module
+    if helper == "python passes":
+        monkeypatch.setattr(adamw_module, "_FS", None)
+    elif adamw_module._FS is None:
+        pytest.skip("_fastscan.so has not been built")
     shapes = SHAPES[:6]
     params = make_params(shapes, torch.bfloat16, "cuda")
     opt = AdamW(params, dtype=torch.bfloat16, storage_device="cuda", seed=9, **HP)
@@ -474,6 +481,16 @@ def test_load_state_dict_in_place_after_the_fast_path_is_armed():
     opt.state[params[0]]["step"] = 40
     mirror.step[0] = 40
     run(6)
+    check(opt, params, mirror)
+    # ... and so are a gradient that disappears and a gradient of another dtype
+    run(7); run(8)
+    assert opt.last_step_info.get("fast")
+    grads = make_grads(shapes, torch.bfloat16, 9)
+    for k, (p, g) in enumerate(zip(params, grads)):
+        p.grad = None if k == 2 else g.cuda()
+    opt.step()
+    mirror.apply(grads, skip=(2,))
+    assert not opt.last_step_info.get("fast")
     check(opt, params, mirror)
 
 
