@@ -51,9 +51,10 @@ void param_ids(py::list params, at::Tensor ids) {
 }
 
 // Every state dict must still hold the cached moment tensors (by identity) and the cached step
-// counter.  Returns -1, or the index of the first state that differs.  With `advance` the
-// counters are then all increased by one (in the dicts and in `steps`).
-int64_t check_states(py::list states, at::Tensor ema_ids, at::Tensor ema_sq_ids, at::Tensor steps, bool advance) {
+// counter.  Returns -1, or the index of the first state that differs (nothing is changed then).
+// With check == false nothing is verified.  Afterwards the counters are all changed by `delta`
+// (+1 for a step, -1 to take one back, 0 to leave them), in the dicts and in `steps`.
+int64_t check_states(py::list states, at::Tensor ema_ids, at::Tensor ema_sq_ids, at::Tensor steps, bool check, int64_t delta) {
   const int64_t n = (int64_t)PyList_GET_SIZE(states.ptr());
   for (const at::Tensor* t : {&ema_ids, &ema_sq_ids, &steps})
     TORCH_CHECK(t->dtype() == at::kLong && t->is_contiguous() && t->numel() == n, "int64[n] expected");
@@ -62,7 +63,7 @@ int64_t check_states(py::list states, at::Tensor ema_ids, at::Tensor ema_sq_ids,
   static PyObject* k_step = PyUnicode_InternFromString("step");
   const int64_t *a = ema_ids.data_ptr<int64_t>(), *b = ema_sq_ids.data_ptr<int64_t>();
   int64_t* s = steps.data_ptr<int64_t>();
-  for (int64_t k = 0; k < n; ++k) {
+  for (int64_t k = 0; check && k < n; ++k) {
     PyObject* st = PyList_GET_ITEM(states.ptr(), k);
     if (!PyDict_Check(st)) return k;
     PyObject* step = PyDict_GetItem(st, k_step);          // borrowed
@@ -71,9 +72,10 @@ int64_t check_states(py::list states, at::Tensor ema_ids, at::Tensor ema_sq_ids,
         PyLong_AsLongLong(step) != s[k])
       return k;
   }
-  if (advance) {
+  if (delta != 0) {
     for (int64_t k = 0; k < n; ++k) {
-      PyObject* next = PyLong_FromLongLong(++s[k]);
+      s[k] += delta;
+      PyObject* next = PyLong_FromLongLong(s[k]);
       PyDict_SetItem(PyList_GET_ITEM(states.ptr(), k), k_step, next);
       Py_DECREF(next);
     }

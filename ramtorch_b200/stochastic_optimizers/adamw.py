@@ -639,8 +639,10 @@ class AdamW(Optimizer):
             scan = f["scan_t"].numpy()
             f["scan"] = scan
             f["mask"] = scan[:, 1] != 0
-            f["p_ptrs_np"] = scan[f["mask"], 0].copy()
-            f["props_np"] = scan[f["mask"], 2].copy()
+            f["all_grads"] = bool(f["mask"].all())
+            f["p_col"] = scan[:, 0].copy()        # data pointer of every parameter
+            f["props_col"] = scan[:, 2].copy()    # gradient properties (0: no gradient)
+            f["props_np"] = scan[f["mask"], 2]
             f["ema_ids_t"] = torch.tensor(list(map(id, f["emas"])), dtype=torch.int64)
             f["ema_sq_ids_t"] = torch.tensor(list(map(id, f["ema_sqs"])), dtype=torch.int64)
             f["steps_t"] = torch.tensor(f["steps"], dtype=torch.int64)
@@ -723,19 +725,20 @@ class AdamW(Optimizer):
         if len(all_params) != len(f["all_ids"]) or _FS.scan_params(all_params, f["ids_t"], f["scan_t"]) >= 0:
             return False
         scan, mask = f["scan"], f["mask"]
-        if not np.array_equal(scan[:, 1] != 0, mask):
-            return False
-        if not (np.array_equal(scan[mask, 0], f["p_ptrs_np"]) and np.array_equal(scan[mask, 2], f["props_np"])):
+        # same parameters' storage, same set of parameters with a gradient, same gradient properties
+        if not (np.array_equal(scan[:, 0], f["p_col"]) and np.array_equal(scan[:, 2], f["props_col"])):
             return False
         states = f["states"]
-        if _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], False) >= 0:
-            return False    # a moment tensor was replaced or a counter edited in place
         plan = self._plans.get(f["index"])
         if plan is None or len(plan.grad_ptrs) != len(states):
             return False
         for g in groups:
             if g["centralization"] != 0:
                 return False
+        # moment tensors and counters as cached (a replaced tensor or an in-place edit of a counter ends
+        # the fast path); the counters advance in the same pass and are taken back if the launch fails
+        if _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], True, 1) >= 0:
+            return False
         rows = []
         for gi, step in f["classes"]:
             g = groups[gi]
@@ -743,16 +746,19 @@ class AdamW(Optimizer):
                                      g["centralization"], self.reference_order, self.shared_draws))
         hyper_arr = (N.Hyper * len(rows))(*rows)
         gptrs = f["gptrs_np"]
-        gptrs[:] = scan[mask, 1]
+        gptrs[:] = scan[:, 1] if f["all_grads"] else scan[mask, 1]
         index = f["index"]
-        with (_NULL_CTX if torch.cuda.current_device() == index else torch.cuda.device(index)):
-            stream = N.stream_ptr(index)
-            N.check(lib.rt_plan_set_grads(plan.handle, gptrs.ctypes.data_as(ctypes.POINTER(N.c_void_p)), stream),
-                    "rt_plan_set_grads")
-            N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(rows), self.seed & (2 ** 64 - 1), stream),
-                    "rt_adamw_sr_multi")
+        try:
+            with (_NULL_CTX if torch.cuda.current_device() == index else torch.cuda.device(index)):
+                stream = N.stream_ptr(index)
+                N.check(lib.rt_plan_set_grads(plan.handle, gptrs.ctypes.data_as(ctypes.POINTER(N.c_void_p)), stream),
+                        "rt_plan_set_grads")
+                N.check(lib.rt_adamw_sr_multi(plan.handle, hyper_arr, len(rows), self.seed & (2 ** 64 - 1), stream),
+                        "rt_adamw_sr_multi")
+        except Exception:
+            _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], False, -1)
+            raise
         f["classes"] = [(gi, step + 1) for gi, step in f["classes"]]
-        _FS.check_states(states, f["ema_ids_t"], f["ema_sq_ids_t"], f["steps_t"], True)   # counters += 1
         for bucket in self._push_marks:
             bucket.pushed = True
         self.last_step_info = dict(launches=plan.launches, resident=len(states), streamed=0, fast=True)
