@@ -301,22 +301,25 @@ def link_frac(h2d_gbs, d2h_gbs, ceiling, world):
     return (h2d_gbs + d2h_gbs) / top, top
 
 
-def nvlink_ceiling(device, rank, world, chunk_bytes=64 << 20, reps=8):
-    """Peer-copy rate per direction per GPU with EVERY rank sending to EVERY peer at once -- the
-    traffic pattern of the fused redistribution: rank r copies one chunk into slot r of each peer's
-    receive buffer with cudaMemcpyAsync (copy engines, one stream per peer), all ranks between the
-    same two barriers.  Returns GB/s leaving (= entering) one GPU, min over ranks."""
+def nvlink_ceiling(device, rank, world, chunk_bytes=256 << 20, reps=8):
+    """Peer-copy rate per direction per GPU, all ranks at once: rank r copies 256 MiB chunks into
+    the receive buffer of rank r+1 (a ring, so every GPU sends to one peer and receives from one)
+    with cudaMemcpyAsync between the same two barriers.  Returns GB/s leaving (= entering) one GPU,
+    min over ranks.  (Copying to ALL peers at once through the copy engines was tried as the
+    ceiling and rejected: at 4 ranks it reaches 375 GB/s per GPU while the optimizer kernel's own
+    peer stores move 684 GB/s -- the copy engines, not the links, limit that pattern.)"""
     import torch
     import torch.distributed as dist
     import torch.distributed._symmetric_memory as symm
-    recv = symm.empty(world * chunk_bytes, dtype=torch.uint8, device=device)
+    recv = symm.empty(chunk_bytes, dtype=torch.uint8, device=device)
     handle = symm.rendezvous(recv, dist.group.WORLD)
     ptrs = [int(q) for q in handle.buffer_ptrs]
     src = torch.empty(chunk_bytes, dtype=torch.uint8, device=device)
     rt = ctypes.CDLL("libcudart.so.12")
     rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
     rt.cudaMemcpyAsync.restype = ctypes.c_int
-    streams = [torch.cuda.Stream(device) for _ in range(world)]
+    stream = torch.cuda.Stream(device)
+    peer = (rank + 1) % world
 
     def burst(n):
         torch.cuda.synchronize(device)
@@ -324,15 +327,11 @@ def nvlink_ceiling(device, rank, world, chunk_bytes=64 << 20, reps=8):
         torch.cuda.synchronize(device)
         t0 = time.perf_counter()
         for _ in range(n):
-            for peer in range(world):
-                if peer == rank:
-                    continue
-                rc = rt.cudaMemcpyAsync(ptrs[peer] + rank * chunk_bytes, src.data_ptr(), chunk_bytes, 4,
-                                        streams[peer].cuda_stream)      # 4 = cudaMemcpyDefault
-                if rc != 0:
-                    raise RuntimeError(f"cudaMemcpyAsync to peer {peer} failed: {rc}")
+            rc = rt.cudaMemcpyAsync(ptrs[peer], src.data_ptr(), chunk_bytes, 4, stream.cuda_stream)   # 4 = cudaMemcpyDefault
+            if rc != 0:
+                raise RuntimeError(f"cudaMemcpyAsync to peer {peer} failed: {rc}")
         torch.cuda.synchronize(device)
-        return chunk_bytes * (world - 1) * n / (time.perf_counter() - t0) / 1e9
+        return chunk_bytes * n / (time.perf_counter() - t0) / 1e9
 
     burst(1)
     gbs = burst(reps)
@@ -340,7 +339,7 @@ def nvlink_ceiling(device, rank, world, chunk_bytes=64 << 20, reps=8):
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     dist.barrier()
     del recv, handle
-    return {"gbs_per_direction_per_gpu": t.item(), "pattern": f"{world} ranks, each to all {world - 1} peers at once, "
+    return {"gbs_per_direction_per_gpu": t.item(), "pattern": f"ring of {world} ranks, every rank to its right neighbour at once, "
             f"{chunk_bytes >> 20} MiB chunks, cudaMemcpyAsync, min over ranks"}
 
 
@@ -955,7 +954,7 @@ def main():
         # fused update + redistribution: the kernel also stores every updated bf16 parameter into the
         # other ranks' buffers, so its target time is the slower of the HBM time and the NVLink time
         # (bytes leaving this GPU / the peer-copy rate per direction measured above with every rank
-        # sending at once)
+        # copying to a neighbour at once)
         measured = nvlink and nvlink.get("gbs_per_direction_per_gpu")
         nvlink_peak = measured or NVLINK_FALLBACK_GBS
         # parameters pushed to the peers, plus (fused reduction) this rank's gradients read by the peers
@@ -968,7 +967,7 @@ def main():
                     "achieved": egress / (upd_ms * 1e-3) / 1e9 if link_bound else roofline["achieved"],
                     "peak": nvlink_peak if link_bound else peak, "unit": "GB/s",
                     "frac": target / (upd_ms * 1e-3), "traffic": None, "kernel_ms": upd_ms,
-                    "peak_source": (("peer copies of every rank to every peer at once, measured in this run" if measured
+                    "peak_source": (("peer copies around a ring of all ranks at once, measured in this run" if measured
                                      else "recorded peer-copy rate (not measurable in this run)") if link_bound else which),
                     "nvlink_egress_bytes": egress, "hbm_algorithmic_bytes": bytes_per_elem * per_rank,
                     "target_ms": target * 1e3}
