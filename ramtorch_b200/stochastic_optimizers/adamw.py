@@ -159,7 +159,10 @@ class _DevicePlan:
         self.push_bucket = SP.push_bucket_for(device_index, [d.p for d in descs])
         if self.push_bucket is not None:
             b = self.push_bucket
-            peers = [q for r, q in enumerate(b.peer_ptrs) if r != b.rank]
+            # peers in ring order starting with the right neighbour: at any moment the ranks' stores head
+            # for different GPUs instead of all starting with rank 0
+            world = len(b.peer_ptrs)
+            peers = [b.peer_ptrs[(b.rank + k) % world] for k in range(1, world)]
             push = N.Push()
             push.local_base = b.flat.data_ptr()
             push.bytes = b.flat.numel() * b.flat.element_size()

@@ -462,11 +462,12 @@ def test_special_values_follow_ieee_like_the_checker():
     assert nan.any() and (~nan).sum() > n // 4
 
 
-def _self_peered_step(n, offsets, dev):
+def _self_peered_step(n, offsets, dev, ranks=3, self_rank=0):
     """Drive the ZeRO peer paths of the kernel on ONE GPU through the C ABI: the "peers" are other
-    buffers of the same device (a peer pointer is just an address).  Rank 0 is this rank; two more
-    gradient copies are pulled and summed in rank order, and the updated parameters are pushed
-    into two more parameter buffers."""
+    buffers of the same device (a peer pointer is just an address).  This rank is `self_rank` of
+    `ranks`; the other ranks' gradient copies are pulled and summed in rank order, and the updated
+    parameters are pushed into ranks - 1 more parameter buffers.  (The number of ranks decides how
+    many shared-memory slots the gradient staging ring gets: 4 up to five ranks, 2 at eight.)"""
     import ctypes
     from ramtorch_b200 import _native as N
     lib = N.lib()
@@ -474,15 +475,15 @@ def _self_peered_step(n, offsets, dev):
     total = offsets[-1][0] + offsets[-1][1]
     pflat = (torch.randn(total, device=dev, generator=gen) * 0.02).bfloat16()
     p0 = pflat.clone()
-    gflats = [(torch.randn(total, device=dev, generator=gen) * 1e-3).bfloat16() for _ in range(3)]
-    pcopies = [torch.zeros(total, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    gflats = [(torch.randn(total, device=dev, generator=gen) * 1e-3).bfloat16() for _ in range(ranks)]
+    pcopies = [torch.zeros(total, dtype=torch.bfloat16, device=dev) for _ in range(ranks - 1)]
     m = (torch.randn(total, device=dev, generator=gen) * 1e-3).bfloat16()
     v = (torch.randn(total, device=dev, generator=gen) * 1e-6).abs().bfloat16()
     m0, v0 = m.clone(), v.clone()
     descs = (N.TensorDesc * len(offsets))()
     for k, (off, cnt) in enumerate(offsets):
         d = descs[k]
-        d.p, d.g = pflat.data_ptr() + 2 * off, gflats[0].data_ptr() + 2 * off
+        d.p, d.g = pflat.data_ptr() + 2 * off, gflats[self_rank].data_ptr() + 2 * off
         d.m, d.v = m.data_ptr() + 2 * off, v.data_ptr() + 2 * off
         d.numel, d.tensor_id = cnt, 40 + k
         d.p_dtype = d.g_dtype = d.state_dtype = N.BF16
@@ -490,12 +491,13 @@ def _self_peered_step(n, offsets, dev):
     N.check(lib.rt_plan_create(ctypes.byref(plan), descs, len(offsets), 0), "rt_plan_create")
     try:
         push = N.Push()
-        push.local_base, push.bytes, push.n_peers = pflat.data_ptr(), 2 * total, 2
-        push.peer_base[0], push.peer_base[1] = pcopies[0].data_ptr(), pcopies[1].data_ptr()
+        push.local_base, push.bytes, push.n_peers = pflat.data_ptr(), 2 * total, ranks - 1
+        for k, c in enumerate(pcopies):
+            push.peer_base[k] = c.data_ptr()
         N.check(lib.rt_plan_set_push(plan, ctypes.byref(push)), "rt_plan_set_push")
         pull = N.Pull()
-        pull.local_base, pull.bytes, pull.n_ranks, pull.self_rank = gflats[0].data_ptr(), 2 * total, 3, 0
-        for r in range(3):
+        pull.local_base, pull.bytes, pull.n_ranks, pull.self_rank = gflats[self_rank].data_ptr(), 2 * total, ranks, self_rank
+        for r in range(ranks):
             pull.base[r] = gflats[r].data_ptr()
         N.check(lib.rt_plan_set_pull(plan, ctypes.byref(pull)), "rt_plan_set_pull")
         hyper = (N.Hyper * 1)(N.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, 7, shared_draws=True))
@@ -517,7 +519,7 @@ def _check_self_peered(offsets, result, spots):
             hi = min(cnt, lo + 65536)
             sl = slice(off + lo, off + hi)
             g32 = gflats[0][sl].float()
-            for r in (1, 2):
+            for r in range(1, len(gflats)):
                 g32 = g32 + gflats[r][sl].float()              # rank order, fp32
             ps, ms, vs = to_numpy(p0[sl]), to_numpy(m0[sl]), to_numpy(v0[sl])
             oracle.adamw_sr(ps, g32.cpu().numpy(), ms, vs, oracle.BF16, oracle.F32, oracle.BF16, ho, seed=5,
@@ -527,14 +529,15 @@ def _check_self_peered(offsets, result, spots):
             assert bits_equal(vs, to_numpy(v[sl])) == 0
 
 
-def test_peer_push_and_gradient_pull_paths_on_one_gpu():
+@pytest.mark.parametrize("ranks,self_rank", [(3, 0), (2, 1), (6, 3), (8, 5), (16, 15)])
+def test_peer_push_and_gradient_pull_paths_on_one_gpu(ranks, self_rank):
     dev = torch.device("cuda", 0)
-    sizes = [64, 8192 * 3 + 5, 100000, 7, 20000]
+    sizes = [64, 8192 * 3 + 5, 100000, 7, 20000, 2048 * 9 + 8]
     offsets, cur = [], 0
     for s in sizes:
         offsets.append((cur, s))
         cur += (s + 127) // 128 * 128
-    _check_self_peered(offsets, _self_peered_step(cur, offsets, dev), lambda cnt: [0])
+    _check_self_peered(offsets, _self_peered_step(cur, offsets, dev, ranks, self_rank), lambda cnt: [0])
 
 
 def test_peer_paths_with_long_ctas_on_a_large_tensor():
