@@ -462,7 +462,7 @@ def test_special_values_follow_ieee_like_the_checker():
     assert nan.any() and (~nan).sum() > n // 4
 
 
-def _self_peered_step(n, offsets, dev, ranks=3, self_rank=0):
+def _self_peered_step(n, offsets, dev, ranks=3, self_rank=0, pull_grads=True):
     """Drive the ZeRO peer paths of the kernel on ONE GPU through the C ABI: the "peers" are other
     buffers of the same device (a peer pointer is just an address).  This rank is `self_rank` of
     `ranks`; the other ranks' gradient copies are pulled and summed in rank order, and the updated
@@ -495,11 +495,14 @@ def _self_peered_step(n, offsets, dev, ranks=3, self_rank=0):
         for k, c in enumerate(pcopies):
             push.peer_base[k] = c.data_ptr()
         N.check(lib.rt_plan_set_push(plan, ctypes.byref(push)), "rt_plan_set_push")
-        pull = N.Pull()
-        pull.local_base, pull.bytes, pull.n_ranks, pull.self_rank = gflats[self_rank].data_ptr(), 2 * total, ranks, self_rank
-        for r in range(ranks):
-            pull.base[r] = gflats[r].data_ptr()
-        N.check(lib.rt_plan_set_pull(plan, ctypes.byref(pull)), "rt_plan_set_pull")
+        if pull_grads:
+            pull = N.Pull()
+            pull.local_base, pull.bytes, pull.n_ranks, pull.self_rank = gflats[self_rank].data_ptr(), 2 * total, ranks, self_rank
+            for r in range(ranks):
+                pull.base[r] = gflats[r].data_ptr()
+            N.check(lib.rt_plan_set_pull(plan, ctypes.byref(pull)), "rt_plan_set_pull")
+        else:
+            gflats = [gflats[self_rank]]          # redistribution only: the gradient is this rank's own
         hyper = (N.Hyper * 1)(N.make_hyper(1e-4, (0.9, 0.999), 1e-8, 0.01, 7, shared_draws=True))
         N.check(lib.rt_adamw_sr_multi(plan, hyper, 1, 5, N.stream_ptr(dev)), "rt_adamw_sr_multi")
         torch.cuda.synchronize()
@@ -529,15 +532,16 @@ def _check_self_peered(offsets, result, spots):
             assert bits_equal(vs, to_numpy(v[sl])) == 0
 
 
+@pytest.mark.parametrize("pull_grads", [True, False], ids=["push+pull", "push-only"])
 @pytest.mark.parametrize("ranks,self_rank", [(3, 0), (2, 1), (6, 3), (8, 5), (16, 15)])
-def test_peer_push_and_gradient_pull_paths_on_one_gpu(ranks, self_rank):
+def test_peer_push_and_gradient_pull_paths_on_one_gpu(ranks, self_rank, pull_grads):
     dev = torch.device("cuda", 0)
     sizes = [64, 8192 * 3 + 5, 100000, 7, 20000, 2048 * 9 + 8]
     offsets, cur = [], 0
     for s in sizes:
         offsets.append((cur, s))
         cur += (s + 127) // 128 * 128
-    _check_self_peered(offsets, _self_peered_step(cur, offsets, dev, ranks, self_rank), lambda cnt: [0])
+    _check_self_peered(offsets, _self_peered_step(cur, offsets, dev, ranks, self_rank, pull_grads), lambda cnt: [0])
 
 
 def test_peer_paths_with_long_ctas_on_a_large_tensor():
@@ -545,5 +549,7 @@ def test_peer_paths_with_long_ctas_on_a_large_tensor():
     dev = torch.device("cuda", 0)
     n = (1 << 29) + 8200
     offsets = [(0, n)]
-    res = _self_peered_step(n, offsets, dev)
-    _check_self_peered(offsets, res, lambda cnt: [0, 8 * 4097, 32768 * 1000 + 8192, cnt // 2 + 24, cnt - 65536])
+    for pull_grads in (True, False):
+        res = _self_peered_step(n, offsets, dev, pull_grads=pull_grads)
+        _check_self_peered(offsets, res, lambda cnt: [0, 8 * 4097, 32768 * 1000 + 8192, cnt // 2 + 24, cnt - 65536])
+        del res
