@@ -109,8 +109,8 @@ typedef struct rt_hyper {
 #define RT_HYPER_SHARED_DRAWS 2u
 /* den and p' in the reference's operation order (see "Arithmetic contract"): one IEEE square
  * root and two IEEE divisions per element.  Bit-identical to the reference's vectorised CPU step
- * in all but ~1e-4 of the elements (where ATen's sqrt is itself not correctly rounded); about a
- * quarter slower than the default when every operand is bf16. */
+ * in all but ~1e-4 of the elements (where ATen's sqrt is itself not correctly rounded); about
+ * 15 % slower than the default when every operand is bf16. */
 #define RT_HYPER_REFERENCE_ORDER 4u
 
 /* Fill an rt_hyper from the constructor-level values, in double precision, as
