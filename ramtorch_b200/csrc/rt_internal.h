@@ -27,7 +27,7 @@ struct DevTensor {
 constexpr uint32_t kVecOk = 1u;  // all four pointers are 16-byte aligned
 constexpr int kChunkShiftBit = 8;  // flags bits 8..11: a CTA covers (kPieceElems << shift) elements
 constexpr int64_t kBigLaunchChunks = 65536;       // launches of at least this many 8192-element chunks ...
-constexpr int64_t kLongTensorElems = 1 << 20;     // ... give tensors at least this long the longer CTAs
+constexpr int64_t kLongTensorElems = 1 << 16;     // ... give tensors at least this long the longer CTAs
 
 // Peer copies of a shared parameter region (kernel argument; n == 0 disables).
 struct PushTable {
