@@ -545,7 +545,7 @@ def test_peer_push_and_gradient_pull_paths_on_one_gpu(ranks, self_rank, pull_gra
 
 
 def test_peer_paths_with_long_ctas_on_a_large_tensor():
-    """2^29 + 8200 elements: enough 8192-element pieces for the four-piece CTAs, with a ragged end."""
+    """2^29 + 8200 elements: enough elements for the launch to use its longer CTAs (16384 elements), with a ragged end."""
     dev = torch.device("cuda", 0)
     n = (1 << 29) + 8200
     offsets = [(0, n)]
