@@ -981,7 +981,7 @@ def main():
     # ZeRO-2 reduce-scatter on its own and the full ZeRO step (reduction + update + redistribution)
     rs = None
     full = None
-    if world > 1 and wl == "c2" and not fused:
+    if world > 1 and wl in ("c2", "c3") and not fused:
         rs = measure_resident(wl, args, device, rank, world, steps=5, warmup=warmup, elems=args.elems,
                               measure_reduce_scatter=True, balance=args.balance)["rs_ms"]
         f1 = measure_resident(wl, args, device, rank, world, steps=max(5, args.steps // 2), warmup=warmup,

@@ -30,9 +30,10 @@ PARAM_IDS_KEY = "rt_param_ids"
 
 def grad_bucket_bytes() -> int:
     """Target size of one gradient sub-bucket (bytes of flat buffer, all ranks' parts together):
-    256 MiB unless RT_ZERO2_BUCKET_MB says otherwise.  Large enough for NCCL to run at link speed,
-    small enough that the first reduce-scatter starts early in backward."""
-    return max(256, int(float(os.environ.get("RT_ZERO2_BUCKET_MB", "256")) * (1 << 20)))
+    512 MiB unless RT_ZERO2_BUCKET_MB says otherwise.  Small enough that the first reduce-scatter
+    starts early in backward; large enough that NCCL runs near link speed (measured on two GPUs,
+    4 GiB in all: one call 4.5 ms, four calls of 1 GiB 4.9 ms, sixteen of 256 MiB 5.5 ms)."""
+    return max(256, int(float(os.environ.get("RT_ZERO2_BUCKET_MB", "512")) * (1 << 20)))
 
 
 class SubBucket:

@@ -5,7 +5,7 @@ The reference registers, on every parameter of every rank's groups, a hook that 
 contract a training loop relies on is: after ``backward``, the owner's gradient of each parameter
 it owns is the SUM over ranks.  Here that is delivered by in-place NCCL ``reduce_scatter``s over a
 flat gradient buffer per (device, dtype): ``p.grad`` of every parameter is a view into it and
-autograd accumulates in place.  The buffer is cut into pieces of about 256 MiB in the order in
+autograd accumulates in place.  The buffer is cut into pieces of about 512 MiB in the order in
 which backward completes them; the hook of the last gradient of a piece launches that piece's
 reduce-scatter at once, so the reduction overlaps the rest of backward (as the reference's
 per-tensor reduce does) while still moving a few large messages instead of one per tensor.
