@@ -60,6 +60,46 @@ def test_flat_layout_is_owner_ordered_equal_segments_and_keeps_values():
     assert isinstance(plan_for(plain), ShardPlan) and plan_for(plain) is plan_for(plain)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("balance", ["count", "bytes"])
+def test_gradient_pieces_cover_every_gradient_once_and_stay_balanced(world, balance, monkeypatch):
+    """Layout of the flat gradient buffer for a Llama-like list (meta tensors, no memory): every
+    gradient lies in exactly one piece, inside its owner's part; parts of a piece are equally long;
+    pieces follow the order in which backward completes the parameters; and a piece is never mostly
+    padding (the rule that keeps one huge tensor from forming a piece of empty parts)."""
+    monkeypatch.setenv("RT_ZERO2_BUCKET_MB", "8")
+    shapes = [(3200, 512)] + [s for _ in range(6) for s in [(512, 512)] * 4 + [(1376, 512)] * 2 + [(512, 1376), (512,), (512,)]]
+    shapes += [(512,), (3200, 512)]
+    params = [torch.empty(s, dtype=torch.bfloat16, device="meta") for s in shapes]
+    rpg = create_zero_param_groups([{"params": params}], world, balance=balance)
+    plan = plan_for(rpg)
+    (b,) = plan.buckets.values()
+    total = plan._layout_grad_pieces(b)
+    spans = sorted((b.goffset[k], b.goffset[k] + p.numel()) for k, p in enumerate(b.params))
+    assert all(x[1] <= y[0] for x, y in zip(spans, spans[1:])) and spans[-1][1] <= total
+    useful = sum(p.numel() for p in params)
+    if balance == "bytes":
+        assert total <= 1.35 * useful                               # bounded padding overall
+    held = [0] * len(b.subs)
+    for k, p in enumerate(b.params):
+        held[b.sub_of[k]] += (p.numel() + 127) // 128 * 128
+    for sub, inside in list(zip(b.subs, held))[:-1]:                # every piece but the (merged) last
+        assert (sub.part * world - inside) * 8 < sub.part * world
+    for k, p in enumerate(b.params):
+        sub = b.subs[b.sub_of[k]]
+        lo = sub.start + b.owner[k] * sub.part
+        assert lo <= b.goffset[k] and b.goffset[k] + p.numel() <= lo + sub.part
+        assert b.goffset[k] % 128 == 0                               # 256-byte aligned views
+    assert [s.start for s in b.subs] == sorted(s.start for s in b.subs)
+    assert all(b.subs[i].start + b.subs[i].part * world == b.subs[i + 1].start for i in range(len(b.subs) - 1))
+    # backward order: a parameter registered later never sits in a later piece than one registered earlier
+    by_order = sorted(range(len(b.params)), key=lambda k: b.order[k])
+    pieces_in_registration_order = [b.sub_of[k] for k in by_order]
+    assert pieces_in_registration_order == sorted(pieces_in_registration_order, reverse=True)
+    if world == 2:
+        assert len(b.subs) >= 2                                      # 44 MB of gradients, 8 MiB target
+
+
 def test_hook_dict_protocol():
     t = torch.zeros(2)
     a = helpers.register_ramtorch_hook(t, lambda g: g * 2, "_ramtorch_zero_2_hooks")
